@@ -1,0 +1,371 @@
+"""Benchmark of the fused multi-feature embedding-bag forward.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg3]
+
+One "step" = one fused forward over one synthetic batch of the workload
+(default: the heavy-tailed 200-feature fp16 configuration, batch 16384, about
+120 GB of tables replicated on every GPU; ranks split the batch stream, no
+collective on the data path).  Rank 0 prints one JSON line:
+
+  value     whole-job samples/s with the batch already resident in HBM
+  e2e       the same through the host-buffer call (H2D of indices/offsets and D2H
+            of the pooled output inside the timed region)
+  roofline  algorithmic bytes (gathered rows + indices + offsets) of one launch
+            divided by the fused kernel's mean CUDA-event duration, against the
+            measured HBM copy bandwidth in MEASURED_PEAKS.json
+  cpu_baseline  torch.nn.functional.embedding_bag(mode='sum') on the host cores
+            on a bounded sample of the same batch (reported only)
+
+`--impl reference` times that CPU path alone (the reference has no CPU
+implementation of its own; the benchmark definition names torch EmbeddingBag
+on the host cores as its CPU path).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np
+
+METRIC = "fused_embedding_bag_samples_per_s"
+UNIT = "samples/s"
+WORKLOADS = {"cfg1": 1, "cfg2": 2, "cfg3": 3, "cfg4": 4, "cfg5": 5}
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=100)
+    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    p.add_argument("--workload", choices=sorted(WORKLOADS), default="cfg3")
+    p.add_argument("--row-scale", type=float, default=1.0, help="shrink every table (debugging only; the line says so)")
+    p.add_argument("--batch", type=int, default=0, help="override the batch size (debugging only)")
+    p.add_argument("--batches", type=int, default=4, help="distinct batches rotated through the steps")
+    p.add_argument("--schedules", type=str, default="", help="JSON file written by the tuner (default: tuned/<workload>.json if present)")
+    p.add_argument("--occupancy", type=int, default=0)
+    p.add_argument("--kind", type=str, default="", help="force one schedule kind for every feature (debugging)")
+    p.add_argument("--unroll", type=int, default=0)
+    p.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU baseline budget")
+    p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--no-e2e", action="store_true")
+    return p.parse_args()
+
+
+# ---------------------------------------------------------------------------
+# clocks (read-only NVML polling during the timed regions)
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {
+        0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+        0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+        0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting",
+    }
+
+    def __init__(self, index: int):
+        self.samples, self.reason_bits = [], 0
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                try:
+                    bits = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                except Exception:
+                    bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                self.reason_bits |= int(bits) & ~0x1
+            except Exception:
+                pass
+            self._stop.wait(0.02)
+
+    def start(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["nvml_unavailable"]}
+        reasons = [name for bit, name in self.REASONS.items() if self.reason_bits & bit]
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz, "reasons": reasons,
+                "samples": len(self.samples)}
+
+
+# ---------------------------------------------------------------------------
+# CPU path (reported baseline and the reference arm)
+# ---------------------------------------------------------------------------
+def cpu_sample(cfg, values, offsets, bags: int):
+    """First `bags` bags of every feature with tables compacted to the rows they touch
+    (the full tables exist only on the GPU); returns (tables, values, offsets) for the oracle."""
+    from recflex_b200 import synth
+
+    tabs, vals, offs = [], [], []
+    for fs, v, o in zip(cfg.features, values, offsets):
+        o = np.asarray(o[: bags + 1], dtype=np.int64)
+        v = np.asarray(v[: o[-1]], dtype=np.int64)
+        uniq, inv = np.unique(v, return_inverse=True)
+        if len(uniq) == 0:
+            uniq = np.zeros(1, dtype=np.int64)
+        tabs.append(synth.synth_rows(fs.seed, uniq, fs.dim, fs.dtype))
+        vals.append(inv.astype(np.int64))
+        offs.append(o)
+    return tabs, vals, offs
+
+
+def time_cpu(cfg, values, offsets, seconds: float, steps: int = 0, warmup: int = 1):
+    import torch
+
+    from oracle import oracle
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    bags = min(1024, len(offsets[0]) - 1)
+    tabs, vals, offs = cpu_sample(cfg, values, offsets, bags)
+    tabs_t = [torch.from_numpy(t).float() for t in tabs]
+    vals_t = [torch.from_numpy(v) for v in vals]
+    offs_t = [torch.from_numpy(o) for o in offs]
+    for _ in range(max(1, warmup)):
+        oracle.pool_torch(tabs_t, vals_t, offs_t)
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        oracle.pool_torch(tabs_t, vals_t, offs_t)
+        reps += 1
+        el = time.perf_counter() - t0
+        if (steps and reps >= steps) or (not steps and el >= seconds):
+            break
+        if steps and el > 240:
+            break
+    return {
+        "value": reps * bags / el,
+        "unit": UNIT,
+        "cores": cores,
+        "kind": "port",
+        "sample": f"torch.nn.functional.embedding_bag(mode='sum') per feature, fp32, {cores} threads; first {bags} bags of "
+                  f"each of {len(cfg.features)} features of one batch, tables compacted to the rows touched; "
+                  f"{reps} passes in {el:.1f} s",
+        "ms_per_step": el / reps * 1e3,
+        "reps": reps,
+    }
+
+
+def run_reference(args):
+    """CPU arm: rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from recflex_b200 import synth
+
+    cfg = synth.make_config(WORKLOADS[args.workload], row_scale=args.row_scale, batch=args.batch or None)
+    values, offsets = synth.gen_batch(cfg, seed=0)
+    res = time_cpu(cfg, values, offsets, args.cpu_seconds, steps=args.steps, warmup=args.warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": res["reps"], "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(cfg, args),
+        "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(cfg, args):
+    return {
+        "workload": cfg.name,
+        "features": len(cfg.features),
+        "batch_per_gpu": cfg.batch,
+        "table_dtype": cfg.features[0].dtype,
+        "table_gb_per_gpu": round(cfg.table_bytes / 1e9, 2),
+        "output_units": cfg.output_units,
+        "partitioning": "tables replicated on every GPU, each rank pools its own batches (no data-path collective)",
+        "l2": f"inputs larger than L2: {cfg.table_bytes / 1e9:.0f} GB of tables, {args.batches} distinct batches rotated",
+        "row_scale": args.row_scale,
+    }
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from recflex_b200 import synth
+    from recflex_b200.rec_modules import FeatEmbed, Schedule
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the fused forward has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    cfg = synth.make_config(WORKLOADS[args.workload], row_scale=args.row_scale, batch=args.batch or None)
+    B, F = cfg.batch, len(cfg.features)
+    tables = synth.make_tables_device(cfg, dev)
+    torch.cuda.synchronize()
+    mod = FeatEmbed(dev, embed_tables=tables)
+
+    sched_path = args.schedules or os.path.join(ROOT, "recflex_b200", "tuned", f"{args.workload}.json")
+    sched_note = "library defaults"
+    if args.kind:
+        mod.set_schedules([Schedule(args.kind, args.unroll) for _ in range(F)], occupancy=args.occupancy)
+        sched_note = f"forced {args.kind} unroll {args.unroll}"
+    elif os.path.exists(sched_path):
+        with open(sched_path) as f:
+            tuned = json.load(f)
+        if len(tuned["schedules"]) == F:
+            mod.set_schedules([Schedule.from_json(s) for s in tuned["schedules"]],
+                              occupancy=args.occupancy or tuned.get("occupancy", 0))
+            sched_note = f"tuned ({os.path.relpath(sched_path, ROOT)})"
+    elif args.occupancy:
+        mod.set_schedules(None, occupancy=args.occupancy)
+    _, occupancy = mod.get_schedules()
+
+    # distinct batches, different on every rank; kept packed on the host (pinned) and on the device
+    host_v, host_o, dev_v, dev_o, alg_bytes = [], [], [], [], []
+    first = None
+    for i in range(args.batches):
+        values, offsets = synth.gen_batch(cfg, seed=1000 * rank + i)
+        if first is None:
+            first = (values, offsets)
+        alg_bytes.append(synth.algorithmic_bytes(cfg, offsets, 4))
+        pv, po = synth.pack_batch(values, offsets)
+        hv, ho = torch.from_numpy(pv).pin_memory(), torch.from_numpy(po).pin_memory()
+        host_v.append(hv)
+        host_o.append(ho)
+        dev_v.append(hv.to(dev))
+        dev_o.append(ho.to(dev))
+    out = torch.empty((B, cfg.output_units), dtype=torch.float32, device=dev)
+    host_out = torch.empty((B, cfg.output_units), dtype=torch.float32).pin_memory()
+    nb = args.batches
+
+    for i in range(max(3, args.warmup)):
+        mod.forward_packed(dev_v[i % nb], dev_o[i % nb], out=out)
+    mod.check_status()
+
+    sampler = ClockSampler(local_rank)
+    # ---- timed region A: inputs resident in HBM ----
+    mod.kernel_timing(True)
+    K = args.steps
+    barrier()
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(K):
+        mod.forward_packed(dev_v[i % nb], dev_o[i % nb], out=out)
+    ev1.record()
+    barrier()
+    t_dev = ev0.elapsed_time(ev1) * 1e-3
+    ktimes = []
+    # the event ring holds 256 launches; longer runs time the first 256
+    ktimes = mod.kernel_times()
+    mod.kernel_timing(False)
+
+    # ---- timed region B: host buffers in, host result out ----
+    t_e2e = None
+    if not args.no_e2e:
+        for i in range(2):
+            mod.forward_host(host_v[i % nb], host_o[i % nb], out=host_out)
+        barrier()
+        ev2, ev3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev2.record()
+        for i in range(K):
+            mod.forward_host(host_v[i % nb], host_o[i % nb], out=host_out)
+        ev3.record()
+        barrier()
+        t_e2e = ev2.elapsed_time(ev3) * 1e-3
+    sampler.stop()
+
+    if world > 1:
+        t = torch.tensor([t_dev, t_e2e or 0.0], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        t_dev, t_e2e_max = float(t[0]), float(t[1])
+        t_e2e = t_e2e_max if t_e2e is not None else None
+
+    if rank == 0:
+        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        if os.path.exists(peaks_path):
+            with open(peaks_path) as f:
+                peak, peak_src = float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+        else:
+            peak, peak_src = 6650.0, "fallback"
+        k_ms = statistics.mean(ktimes) if ktimes else None
+        mean_bytes = statistics.mean(alg_bytes[i % nb] for i in range(min(K, 256)))
+        achieved = mean_bytes / (k_ms * 1e-3) / 1e9 if k_ms else None
+        h2d = int(host_v[0].numel() * 4 + host_o[0].numel() * 4)
+        d2h = int(B * cfg.output_units * 4)
+        line = {
+            "metric": METRIC, "value": world * K * B / t_dev, "unit": UNIT, "n_gpus": world, "steps": K,
+            "warmup": max(3, args.warmup), "ms_per_step": t_dev / K * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {**workload_config(cfg, args), "schedules": sched_note, "occupancy": occupancy,
+                       "index_dtype": "int32"},
+            "roofline": {
+                "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak if achieved else None, "traffic": None,
+                "kernel": "eb_fused_kernel", "kernel_ms": k_ms, "algorithmic_bytes_per_launch": mean_bytes,
+                "peak_source": peak_src,
+            },
+            "e2e": {"value": world * K * B / t_e2e if t_e2e else None, "unit": UNIT, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": t_e2e / K * 1e3 if t_e2e else None},
+            "gpu_launches": 2 * K,
+            "clocks": sampler.summary(),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            res = time_cpu(cfg, first[0], first[1], args.cpu_seconds)
+            line["cpu_baseline"] = {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,230 @@
+/*
+ * recflex_b200.h — C ABI of librecflex_b200.so: the fused multi-feature
+ * embedding-bag forward (sum pooling, per-feature outputs concatenated into
+ * one [batch, sum(dim_f)] fp32 matrix) for NVIDIA B200 (sm_100a).
+ *
+ * Conventions
+ *  - Every function returns 0 on success and a negative EB_ERR_* code on
+ *    failure; eb_last_error() returns a thread-local message for the last
+ *    failure.  No C++ exception crosses this boundary.
+ *  - The caller owns every buffer.  The library allocates device memory only
+ *    inside eb_create() (a descriptor table of a few KB per handle, released
+ *    by eb_destroy()); all per-call scratch lives in the caller's `workspace`.
+ *  - Every launch goes to the `stream` argument (a cudaStream_t passed as
+ *    void*, so that this header needs no CUDA include).
+ *  - A handle is not thread-safe: use one handle per host thread / stream.
+ *
+ * Each entry point names the piece of the RecFlex reference it replaces
+ * (paths are relative to the RecFlex repository root).
+ */
+#ifndef RECFLEX_B200_H_
+#define RECFLEX_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define EB_OK 0
+#define EB_ERR_INVALID_ARG (-1)
+#define EB_ERR_CUDA (-2)
+#define EB_ERR_WORKSPACE_TOO_SMALL (-3)
+#define EB_ERR_BAD_INPUT (-4)      /* device-side input check failed (index out of range, offsets not monotone) */
+#define EB_ERR_UNSUPPORTED (-5)
+#define EB_ERR_TOO_LARGE (-6)
+
+/* table_dtype values */
+#define EB_F32 0
+#define EB_F16 1
+/* index_dtype values (values and offsets share one dtype, as in torch.nn.EmbeddingBag) */
+#define EB_I32 0
+#define EB_I64 1
+
+/*
+ * Per-feature schedule kinds.  They play the role of the reference's schedule
+ * classes (examples/schedules/*.py + examples/csrc/include/*_kernel.cuh):
+ *   EB_SCHED_GROUP  a sub-warp group of `row_bytes/16` lanes owns one bag and
+ *                   walks it serially (thread-per-bag for 16-byte rows); no
+ *                   cross-lane reduction.  Replaces ws::SparseSegmentReduce
+ *                   (warp_per_sample_kernel.cuh:10-82) and the one-hot row copy
+ *                   onehot::GatherSegments (onehot_kernel.cuh:14-87).
+ *   EB_SCHED_WARP   a whole warp owns one bag; its 32/(row_bytes/16) row slots
+ *                   split the bag and are combined with warp shuffles.
+ *                   Replaces obms::SparseSegmentReduce
+ *                   (one_block_multi_sample_kernel.cuh:16-108).
+ *   EB_SCHED_FLAT   a warp streams the flattened index list of a run of bags,
+ *                   keeps `unroll` rows per lane in flight regardless of bag
+ *                   boundaries and resolves the boundaries with a segmented
+ *                   warp reduction.  Replaces rbk::SparseSegmentSum
+ *                   (reduce_by_key_kernel.cuh:185-366) without its inter-block
+ *                   barrier and without leaving empty bags unwritten.
+ *   EB_SCHED_AUTO   let the library choose from dim, dtype and mean bag length.
+ */
+#define EB_SCHED_AUTO 0
+#define EB_SCHED_GROUP 1
+#define EB_SCHED_WARP 2
+#define EB_SCHED_FLAT 3
+
+typedef struct eb_handle eb_handle;
+
+/* One feature's schedule = the reference's (ScheduleBase subclass, params NamedTuple)
+ * pair (RecFlex/code_emitter/schedule_base.py:54-87). */
+typedef struct eb_schedule {
+  int32_t kind;          /* EB_SCHED_* */
+  int32_t unroll;        /* rows kept in flight per lane: 1, 2, 4 or 8 (0 = auto) */
+  int32_t vec_bytes;     /* bytes per lane per row load: 16 (0 = auto; rows that are not 16-byte multiples use the element-wise fallback) */
+  int32_t bags_per_tile; /* bags bound to one warp per tile; 0 = chosen on the device from the batch's mean bag length */
+} eb_schedule;
+
+/*
+ * Create a handle for `num_features` embedding tables that live on `device`.
+ * rows[f] x dims[f] row-major, dtype table_dtype[f] (EB_F32 / EB_F16),
+ * table_ptrs[f] = device pointer.  The tables must stay allocated and in place
+ * for the life of the handle.
+ * Replaces FeatEmbed.__init__ + torch.ops.recom.get_gpu_pointers_array
+ * (RecFlex/rec_modules.py:57-76, RecFlex/sched_basic_csrc/gpu_pointers_array.cc:16-25).
+ */
+int eb_create(eb_handle** out, int device, int num_features, const int64_t* rows,
+              const int32_t* dims, const int32_t* table_dtype,
+              const void* const* table_ptrs);
+
+/* Release the handle and its device descriptor table. */
+int eb_destroy(eb_handle* h);
+
+/* Sum of dims = width of one output row (FeatEmbed.output_units, rec_modules.py:74-76). */
+int eb_output_units(const eb_handle* h, int64_t* units);
+
+/*
+ * Set every feature's schedule and the CTAs-per-SM occupancy (1..8, 0 = keep)
+ * of the fused kernel.  Replaces the code generation + compilation of one
+ * FusedKnl per schedule assignment (RecFlex/code_emitter/codegen.py:221-383,
+ * 474-494): every schedule variant is already compiled into the library.
+ */
+int eb_set_schedules(eb_handle* h, const eb_schedule* per_feature, int occupancy);
+
+/* Read back the schedules in force (after AUTO resolution) and the occupancy. */
+int eb_get_schedules(const eb_handle* h, eb_schedule* per_feature, int* occupancy);
+
+/* Bytes of device scratch one forward call needs (independent of the batch size). */
+int eb_workspace_bytes(const eb_handle* h, size_t* bytes);
+
+/*
+ * Persistent CTAs the fused kernel runs at `occupancy` CTAs per SM
+ * (0 = the handle's current occupancy).  Replaces
+ * torch.ops.recom.get_max_concurrent_blocks
+ * (RecFlex/code_emitter/codegen.py:446-452, RecFlex/sched_basic_csrc/include/utils.cuh:6-21).
+ */
+int eb_max_concurrent_ctas(const eb_handle* h, int occupancy, int* ctas);
+
+/*
+ * The fused forward.  values_ptrs[f] / offsets_ptrs[f] are DEVICE pointers to
+ * feature f's indices (nnz_f entries) and bag offsets (batch entries, or
+ * batch+1 when offsets_have_end != 0, the last one being nnz_f).  nnz[f] is a
+ * HOST array with each feature's index count (ignored, may be NULL, when
+ * offsets_have_end != 0).  out is a DEVICE fp32 matrix [batch, out_ld] whose
+ * first eb_output_units() columns receive the pooled rows (out_ld >= units
+ * lets a caller write into a slice of a wider buffer).  Every element of those
+ * columns is written; empty bags pool to 0.
+ * Replaces recom_host.preprocess's tiling/task mapping + torch.ops.recom.process
+ * (RecFlex/code_emitter/codegen.py:90-181, 387-444;
+ *  RecFlex/sched_basic_csrc/task_mapping.cu:6-18) — the block-to-feature binding
+ * is computed on the device from the batch itself.
+ */
+int eb_forward(eb_handle* h, int64_t batch, const void* const* values_ptrs,
+               const void* const* offsets_ptrs, const int64_t* nnz, int index_dtype,
+               int offsets_have_end, float* out, int64_t out_ld, void* workspace,
+               size_t workspace_bytes, void* stream);
+
+/*
+ * Same, for one packed (jagged) batch: `values` holds all features' indices
+ * back to back in feature order, `offsets` is a [num_features, batch+1] matrix
+ * of per-feature offsets (each row starts at 0 and ends at nnz_f).  Both are
+ * DEVICE pointers; nothing is uploaded per call.
+ * Replaces the packed d_arg_buffers / d_arg_buffer_offsets arguments of
+ * FusedKnl (RecFlex/code_emitter/codegen.py:144-160, 318-331).
+ */
+int eb_forward_packed(eb_handle* h, int64_t batch, const void* values, const void* offsets,
+                      int index_dtype, float* out, int64_t out_ld, void* workspace,
+                      size_t workspace_bytes, void* stream);
+
+/*
+ * End-to-end call with HOST buffers (pinned memory recommended): copies the
+ * packed batch to `staging` (device scratch of at least eb_host_staging_bytes),
+ * runs the fused forward and copies the [batch, units] result back to host_out.
+ * Returns after enqueueing; the caller synchronises `stream`.
+ * Replaces FeatProcessEmbed.forward's upload + launch
+ * (RecFlex/rec_modules.py:27-42, 127-133).
+ */
+int eb_forward_host(eb_handle* h, int64_t batch, const void* host_values, int64_t total_nnz,
+                    const void* host_offsets, int index_dtype, float* host_out,
+                    void* staging, size_t staging_bytes, void* workspace,
+                    size_t workspace_bytes, void* stream);
+int eb_host_staging_bytes(const eb_handle* h, int64_t batch, int64_t total_nnz,
+                          int index_dtype, size_t* bytes);
+
+/*
+ * The fused forward with per-feature device time, the counterpart of
+ * `timing=True` (RecFlex/code_emitter/codegen.py:301-316, 396-401;
+ * RecFlex/rec_modules.py:96-109): each tile's globaltimer delta is summed per
+ * feature.  per_feature_ns is a HOST array of num_features doubles; the call
+ * synchronises `stream`.
+ */
+int eb_forward_timed(eb_handle* h, int64_t batch, const void* const* values_ptrs,
+                     const void* const* offsets_ptrs, const int64_t* nnz, int index_dtype,
+                     int offsets_have_end, float* out, int64_t out_ld, void* workspace,
+                     size_t workspace_bytes, void* stream, double* per_feature_ns);
+
+/*
+ * Kernel timing.  eb_kernel_timing(h, 1) makes every later forward record a
+ * CUDA event pair around its fused-kernel launch (a ring of 256 pairs; the
+ * binding kernel is outside the pair).  eb_kernel_times() waits for the
+ * recorded pairs, writes the elapsed milliseconds of each launch since the
+ * previous read (oldest first, at most `cap`) and clears the ring.  This is the
+ * in-process counterpart of the reference's global-stage measurement, the
+ * FusedKnl total from `nsys stats --report gpukernsum`
+ * (RecFlex/parser.py:71-85, RecFlex/tuning/measure.py:98-122).
+ */
+int eb_kernel_timing(eb_handle* h, int enable);
+int eb_kernel_times(eb_handle* h, float* ms, int cap, int* count);
+
+/*
+ * Copy the device status word of the last forward that used `workspace` and
+ * return EB_ERR_BAD_INPUT when the kernel met an index outside [0, rows) or a
+ * decreasing offset (such entries are skipped, never dereferenced).
+ * Synchronises `stream`.  The reference performs no such check.
+ */
+int eb_check_status(eb_handle* h, void* workspace, void* stream);
+
+/*
+ * Fill a table with the library's counter-based synthetic weights: element
+ * (row, col) of a table with `seed` is a fixed integer hash mapped to an
+ * approximately normal value of standard deviation `std`; any row can be
+ * regenerated on any device or on the CPU without storing the table.
+ * Stands in for torch.randn table creation (RecFlex/rec_modules.py:64-68).
+ */
+int eb_fill_table(void* table, int64_t rows, int32_t dim, int32_t table_dtype, uint64_t seed,
+                  float std, int device, void* stream);
+
+/*
+ * Host-side parser of the reference's text input: `text` holds `batch` lines
+ * separated by '\n' (one bag per line, indices separated by any non-digit
+ * character, an empty line is an empty bag).  Writes the indices to values_out
+ * (capacity values_cap) and batch+1 offsets to offsets_out; *nnz_out receives
+ * the index count.  Replaces ws::StringSplitToInt
+ * (examples/csrc/warp_per_sample_preprocess.cu:6-38).
+ */
+int eb_parse_bags(const char* text, size_t text_len, int64_t batch, int32_t* values_out,
+                  int64_t values_cap, int32_t* offsets_out, int64_t* nnz_out);
+
+/* Message of the calling thread's last failure ("" if none). */
+const char* eb_last_error(void);
+
+/* Library version string and the SM architecture it was compiled for. */
+const char* eb_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RECFLEX_B200_H_ */

@@ -1,0 +1,181 @@
+// eb_bind_kernel: one CTA; turns the batch's per-feature index counts into
+// tile sizes, a heaviest-first feature order and an exclusive prefix sum of
+// tile counts: the run-time block-to-feature binding.  Replaces the host
+// GetTaskMapping (RecFlex/sched_basic_csrc/task_mapping.cu:6-18) and the
+// per-schedule num_tiles / num_blocks arithmetic of the host preprocess
+// (examples/csrc/*_preprocess.cu).
+// eb_fill_kernel: counter-based synthetic table weights.
+// Included by exactly one translation unit (eb_launch.cu).
+#pragma once
+#include "eb_common.cuh"
+#include "eb_schedules.cuh"
+
+namespace ebk {
+
+// ---------------------------------------------------------------------------
+// block-wide exclusive scan of one int64 per thread (kBindThreads threads)
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ long long block_excl_scan(long long v, long long* s_warp, long long& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  long long inc = v;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const long long t = __shfl_up_sync(kFull, inc, d);
+    if (lane >= d) inc += t;
+  }
+  __syncthreads();  // s_warp may still be read from a previous call
+  if (lane == 31) s_warp[warp] = inc;
+  __syncthreads();
+  long long w = s_warp[lane];  // kBindThreads / 32 == 32 warps
+  long long winc = w;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const long long t = __shfl_up_sync(kFull, winc, d);
+    if (lane >= d) winc += t;
+  }
+  total = __shfl_sync(kFull, winc, 31);
+  const long long warp_excl = __shfl_sync(kFull, winc - w, warp);
+  return warp_excl + inc - v;
+}
+
+__device__ __forceinline__ int pow2_floor(long long x) {
+  if (x < 1) return 1;
+  if (x > (1 << 20)) x = 1 << 20;
+  return 1 << (31 - __clz((int)x));
+}
+
+__device__ __forceinline__ int tiles_of(int64_t batch, int bpt) { return (int)((batch + bpt - 1) / bpt); }
+
+__global__ void __launch_bounds__(kBindThreads) eb_bind_kernel(LaunchArgs a, int zero_ns) {
+  static_assert(kBindThreads == 1024, "block scan assumes 32 warps");
+  __shared__ long long s_warp[32];
+  __shared__ float s_cost[kMaxLptFeatures];
+  const int tid = threadIdx.x;
+  const int F = a.num_features;
+  const WsLayout L = ws_layout(F);
+  WsHeader* hdr = reinterpret_cast<WsHeader*>(a.ws + L.header);
+  int32_t* tile_prefix = reinterpret_cast<int32_t*>(a.ws + L.tile_prefix);
+  int32_t* order = reinterpret_cast<int32_t*>(a.ws + L.order);
+  int32_t* bpt = reinterpret_cast<int32_t*>(a.ws + L.bags_per_tile);
+  FeatDyn* dyn = reinterpret_cast<FeatDyn*>(a.ws + L.dyn);
+  unsigned long long* feat_ns = reinterpret_cast<unsigned long long*>(a.ws + L.feat_ns);
+  const int isz = a.idx64 ? 8 : 4;
+  const int64_t B = a.batch;
+  uint32_t status = 0;
+
+  // pass 1: index counts, packed-mode pointers, gathered bytes of the batch
+  long long carry = 0, my_bytes = 0;
+  for (int base = 0; base < F; base += kBindThreads) {
+    const int f = base + tid;
+    long long nnz = 0;
+    const char* offp = nullptr;
+    if (f < F) {
+      if (a.packed) {
+        offp = a.packed_offsets + (int64_t)f * (B + 1) * isz;
+        nnz = load_index(offp, B, a.idx64);
+      } else {
+        const FeatDyn d = dyn[f];
+        offp = d.offsets;
+        nnz = a.has_end ? load_index(d.offsets, B, a.idx64) : d.nnz;
+      }
+      if (nnz < 0) { nnz = 0; status |= kStatusBadOffsets; }
+    }
+    long long total;
+    const long long excl = block_excl_scan(nnz, s_warp, total) + carry;
+    carry += total;
+    if (f < F) {
+      if (a.packed) {
+        dyn[f].values = a.packed_values + excl * isz;
+        dyn[f].offsets = offp;
+      }
+      dyn[f].nnz = nnz;
+      my_bytes += nnz * (long long)a.feats[f].row_bytes;
+      if (zero_ns) feat_ns[f] = 0ull;
+    }
+  }
+  long long total_bytes;
+  block_excl_scan(my_bytes, s_warp, total_bytes);
+
+  // pass 2: bags per tile.  Tiles aim at the same gathered bytes so that a
+  // ticket costs about the same whatever the feature; about 16 tiles per warp.
+  long long target = total_bytes / ((long long)a.warps_total * 16);
+  target = target < (16 << 10) ? (16 << 10) : (target > (256 << 10) ? (256 << 10) : target);
+  for (int f = tid; f < F; f += kBindThreads) {
+    const FeatStatic fs = a.feats[f];
+    long long mean_bytes = B > 0 ? dyn[f].nnz * (long long)fs.row_bytes / B : 0;
+    if (mean_bytes < fs.row_bytes) mean_bytes = fs.row_bytes;
+    int n = fs.bags_per_tile > 0 ? fs.bags_per_tile : pow2_floor(target / mean_bytes);
+    const int lo = fs.bags_per_tile > 0 ? 1 : (fs.kind == 1 /*GROUP*/ ? 32 : 1);
+    n = n < lo ? lo : (n > 1024 ? 1024 : n);
+    bpt[f] = n;
+    if (F <= kMaxLptFeatures) s_cost[f] = (float)n * (float)mean_bytes;
+  }
+  __syncthreads();
+
+  // pass 3: heaviest tiles first (longest-processing-time order) to shorten the tail
+  for (int f = tid; f < F; f += kBindThreads) {
+    int rank = f;
+    if (F <= kMaxLptFeatures) {
+      const float c = s_cost[f];
+      rank = 0;
+      for (int g = 0; g < F; ++g) {
+        const float cg = s_cost[g];
+        rank += (cg > c || (cg == c && g < f)) ? 1 : 0;
+      }
+    }
+    order[rank] = f;
+  }
+  __syncthreads();
+
+  // pass 4: exclusive prefix sum of tile counts in that order
+  carry = 0;
+  for (int base = 0; base < F; base += kBindThreads) {
+    const int k = base + tid;
+    const long long t = k < F ? tiles_of(B, bpt[order[k]]) : 0;
+    long long total;
+    const long long excl = block_excl_scan(t, s_warp, total) + carry;
+    carry += total;
+    if (k < F) tile_prefix[k] = (int32_t)excl;
+  }
+  status = __syncthreads_or((int)status);
+  if (tid == 0) {
+    tile_prefix[F] = (int32_t)carry;
+    hdr->ticket = 0;
+    hdr->total_tiles = (uint32_t)carry;
+    hdr->cta_ticket = 0;
+    hdr->cta_tiles = 0;
+    hdr->status = status;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// table fill: counter-based synthetic weights (bit-reproducible on the CPU)
+// ---------------------------------------------------------------------------
+__host__ __device__ inline uint64_t mix64(uint64_t x) {
+  x += 0x9E3779B97F4A7C15ull;
+  x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+  x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+  return x ^ (x >> 31);
+}
+
+// Sum of four 16-bit fields, centred: integer in [-131070, 131070] with
+// standard deviation 65536 * sqrt(4 / 12); one fp32 multiply maps it to the
+// requested scale, so the CPU and the GPU agree to the bit.
+__host__ __device__ inline float synth_weight(uint64_t seed, uint64_t elem, float scale) {
+  const uint64_t h = mix64(seed * 0xD1342543DE82EF95ull + elem);
+  const int s = (int)(h & 0xffff) + (int)((h >> 16) & 0xffff) + (int)((h >> 32) & 0xffff) +
+                (int)((h >> 48) & 0xffff) - 131070;
+  return (float)s * scale;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) eb_fill_kernel(T* table, int64_t elems, uint64_t seed, float scale) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < elems; i += stride) {
+    const float w = synth_weight(seed, (uint64_t)i, scale);
+    if constexpr (sizeof(T) == 2) table[i] = __float2half_rn(w);
+    else table[i] = w;
+  }
+}
+
+}  // namespace ebk

@@ -1,0 +1,97 @@
+// Shared declarations of the fused embedding-bag library: the device-side
+// feature descriptors, the per-call scratch ("workspace") layout and the
+// launch argument block.  Host and device code both include this file.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ebk {
+
+constexpr int kCtaThreads = 256;        // one value for every feature, as in the reference (codegen.py:24-26)
+constexpr int kWarpsPerCta = kCtaThreads / 32;
+constexpr int kMaxOccupancy = 8;        // 2048 threads per SM / 256
+constexpr int kBindThreads = 1024;
+constexpr int kMaxLptFeatures = 2048;   // features beyond this keep their input order
+
+// status bits written by the kernels (never a trap)
+constexpr uint32_t kStatusBadIndex = 1u;    // an index outside [0, rows) was skipped
+constexpr uint32_t kStatusBadOffsets = 2u;  // offsets were clamped to a non-decreasing sequence inside [0, nnz]
+
+// Static per-feature descriptor; lives in device memory owned by the handle.
+struct __align__(16) FeatStatic {
+  const char* table;     // row-major [rows, dim]
+  int64_t rows;
+  int32_t dim;
+  int32_t col_off;       // first output column of this feature
+  int32_t row_bytes;     // dim * sizeof(element)
+  int32_t dtype;         // 0 = f32, 1 = f16
+  int32_t kind;          // EB_SCHED_* after AUTO resolution
+  int32_t unroll;        // 1, 2, 4, 8
+  int32_t lg_group;      // log2(lanes that share one row)
+  int32_t nx;            // column passes (rows wider than 32 lanes' worth)
+  int32_t vec;           // 1 = 16-byte lane loads; 0 = element-wise fallback
+  int32_t bags_per_tile; // 0 = decided per batch on the device
+  int32_t pad_[2];
+};
+static_assert(sizeof(FeatStatic) == 64, "FeatStatic must stay 64 bytes");
+
+// Per-call, per-feature inputs.
+struct __align__(8) FeatDyn {
+  const char* values;
+  const char* offsets;
+  int64_t nnz;
+  int64_t pad_;
+};
+static_assert(sizeof(FeatDyn) == 32, "FeatDyn must stay 32 bytes");
+
+// First 128 bytes of the workspace.
+struct __align__(128) WsHeader {
+  uint32_t ticket;        // next warp tile
+  uint32_t total_tiles;
+  uint32_t cta_ticket;    // next CTA tile (block-per-bag features)
+  uint32_t cta_tiles;
+  uint32_t status;
+  uint32_t pad_[27];
+};
+static_assert(sizeof(WsHeader) == 128, "WsHeader must stay 128 bytes");
+
+// Host/device view of where each array sits inside the workspace.
+struct WsLayout {
+  size_t header, tile_prefix, cta_prefix, order, bags_per_tile, dyn, feat_ns, total;
+};
+
+__host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+__host__ __device__ inline WsLayout ws_layout(int F) {
+  WsLayout l;
+  size_t o = 0;
+  l.header = o;        o += sizeof(WsHeader);
+  l.tile_prefix = o;   o = align_up(o + sizeof(int32_t) * (size_t)(F + 1), 128);
+  l.cta_prefix = o;    o = align_up(o + sizeof(int32_t) * (size_t)(F + 1), 128);
+  l.order = o;         o = align_up(o + sizeof(int32_t) * (size_t)F, 128);
+  l.bags_per_tile = o; o = align_up(o + sizeof(int32_t) * (size_t)F, 128);
+  l.dyn = o;           o = align_up(o + sizeof(FeatDyn) * (size_t)F, 128);
+  l.feat_ns = o;       o = align_up(o + sizeof(unsigned long long) * (size_t)F, 128);
+  l.total = o;
+  return l;
+}
+
+// Everything a launch needs, passed by value as the kernel parameter.
+struct LaunchArgs {
+  const FeatStatic* feats;
+  char* ws;               // workspace base
+  const char* packed_values;   // packed mode only
+  const char* packed_offsets;  // packed mode only: [F, batch + 1]
+  float* out;
+  int64_t out_ld;
+  int64_t batch;
+  int32_t num_features;
+  int32_t idx64;          // values/offsets are int64 (else int32)
+  int32_t has_end;        // offsets carry batch + 1 entries
+  int32_t packed;
+  int32_t out_vec;        // out base and out_ld allow 16-byte stores
+  int32_t warps_total;    // persistent warps of the fused kernel (for tile sizing)
+};
+
+}  // namespace ebk

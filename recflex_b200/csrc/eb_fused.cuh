@@ -1,0 +1,108 @@
+// eb_fused_kernel: persistent CTAs; every warp draws tile tickets, finds the
+// ticket's feature by binary search in the prefix sum that eb_bind_kernel
+// (eb_bind.cuh) left in the workspace and runs that feature's schedule.
+// Replaces the generated FusedKnl dispatcher
+// (RecFlex/code_emitter/codegen.py:318-383).
+#pragma once
+#include "eb_common.cuh"
+#include "eb_schedules.cuh"
+
+namespace ebk {
+
+// ---------------------------------------------------------------------------
+// schedule dispatch
+// ---------------------------------------------------------------------------
+#define EB_DISPATCH_UNROLL(FN, T, V)                          \
+  switch (fs.unroll) {                                        \
+    case 1: FN<T, V, 1>(ctx, b0, b1, lane); break;            \
+    case 2: FN<T, V, 2>(ctx, b0, b1, lane); break;            \
+    case 4: FN<T, V, 4>(ctx, b0, b1, lane); break;            \
+    default: FN<T, V, 8>(ctx, b0, b1, lane); break;           \
+  }
+
+#define EB_DISPATCH_DTYPE(FN)                                 \
+  if (fs.dtype == 1) {                                        \
+    EB_DISPATCH_UNROLL(FN, __half, 8)                         \
+  } else {                                                    \
+    EB_DISPATCH_UNROLL(FN, float, 4)                          \
+  }
+
+template <int OCC, bool TIMING>
+__global__ void __launch_bounds__(kCtaThreads, OCC) eb_fused_kernel(LaunchArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int F = a.num_features;
+  const WsLayout L = ws_layout(F);
+  WsHeader* hdr = reinterpret_cast<WsHeader*>(a.ws + L.header);
+  const int32_t* tile_prefix = reinterpret_cast<const int32_t*>(a.ws + L.tile_prefix);
+  const int32_t* order = reinterpret_cast<const int32_t*>(a.ws + L.order);
+  const int32_t* bpt = reinterpret_cast<const int32_t*>(a.ws + L.bags_per_tile);
+  const FeatDyn* dyn = reinterpret_cast<const FeatDyn*>(a.ws + L.dyn);
+  unsigned long long* feat_ns = reinterpret_cast<unsigned long long*>(a.ws + L.feat_ns);
+  const uint32_t total = hdr->total_tiles;
+
+  uint32_t t = 0;
+  if (lane == 0) t = atomicAdd(&hdr->ticket, 1u);
+  t = __shfl_sync(kFull, t, 0);
+  while (t < total) {
+    // draw the next ticket now; its latency hides behind this tile
+    uint32_t tn = 0;
+    if (lane == 0) tn = atomicAdd(&hdr->ticket, 1u);
+
+    int lo = 0, hi = F;  // tile_prefix[lo] <= t < tile_prefix[hi]
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if ((uint32_t)__ldg(tile_prefix + mid) <= t) lo = mid; else hi = mid;
+    }
+    const int f = __ldg(order + lo);
+    const int64_t tile = (int64_t)(t - (uint32_t)__ldg(tile_prefix + lo));
+    const FeatStatic fs = a.feats[f];
+    const FeatDyn fd = dyn[f];
+    const int n = __ldg(bpt + f);
+    const int64_t b0 = tile * n;
+    const int64_t b1 = (b0 + n) < a.batch ? (b0 + n) : a.batch;
+
+    TileCtx ctx;
+    ctx.table = fs.table;
+    ctx.values = fd.values;
+    ctx.offsets = fd.offsets;
+    ctx.rows = fs.rows;
+    ctx.nnz = fd.nnz;
+    ctx.batch = a.batch;
+    ctx.out = a.out + fs.col_off;
+    ctx.out_ld = a.out_ld;
+    ctx.status = &hdr->status;
+    ctx.dim = fs.dim;
+    ctx.row_bytes = fs.row_bytes;
+    ctx.lg_group = fs.lg_group;
+    ctx.nx = fs.nx;
+    ctx.idx64 = a.idx64 != 0;
+    ctx.has_end = a.has_end != 0;
+    ctx.out_vec = a.out_vec != 0 && (fs.col_off & 3) == 0;
+
+    long long c0 = 0;
+    if (TIMING) c0 = clock64();
+
+    if (!fs.vec) {
+      if (fs.dtype == 1) tile_warp<__half, 1, 4>(ctx, b0, b1, lane);
+      else tile_warp<float, 1, 4>(ctx, b0, b1, lane);
+    } else if (fs.kind == 1) {
+      EB_DISPATCH_DTYPE(tile_group)
+    } else if (fs.kind == 2) {
+      EB_DISPATCH_DTYPE(tile_warp)
+    } else {
+      EB_DISPATCH_DTYPE(tile_flat)
+    }
+
+    if (TIMING) {
+      __syncwarp();
+      const long long c1 = clock64();
+      if (lane == 0) atomicAdd(feat_ns + f, (unsigned long long)(c1 - c0));
+    }
+    t = __shfl_sync(kFull, tn, 0);
+  }
+}
+
+#undef EB_DISPATCH_UNROLL
+#undef EB_DISPATCH_DTYPE
+
+}  // namespace ebk

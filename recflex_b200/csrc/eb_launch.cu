@@ -1,0 +1,49 @@
+// Launchers: pick the fused-kernel instantiation for an occupancy, launch the
+// binding kernel and the table-fill kernel.
+#include "eb_bind.cuh"
+#include "eb_launch.h"
+
+namespace ebk {
+
+static FusedKernel pick(int occ, bool timing) {
+  switch (occ) {
+    case 1: return fused_kernel_occ1(timing);
+    case 2: return fused_kernel_occ2(timing);
+    case 3: return fused_kernel_occ3(timing);
+    case 4: return fused_kernel_occ4(timing);
+    case 5: return fused_kernel_occ5(timing);
+    case 6: return fused_kernel_occ6(timing);
+    case 7: return fused_kernel_occ7(timing);
+    default: return fused_kernel_occ8(timing);
+  }
+}
+
+cudaError_t launch_bind(const LaunchArgs& a, bool zero_feature_times, cudaStream_t st) {
+  eb_bind_kernel<<<1, kBindThreads, 0, st>>>(a, zero_feature_times ? 1 : 0);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_fused(const LaunchArgs& a, int occupancy, bool timing, int grid, cudaStream_t st) {
+  FusedKernel k = pick(occupancy, timing);
+  void* params[] = {const_cast<LaunchArgs*>(&a)};
+  return cudaLaunchKernel(reinterpret_cast<const void*>(k), dim3(grid), dim3(kCtaThreads), params, 0, st);
+}
+
+cudaError_t fused_ctas_per_sm(int occupancy, int* per_sm) {
+  return cudaOccupancyMaxActiveBlocksPerMultiprocessor(per_sm, reinterpret_cast<const void*>(pick(occupancy, false)),
+                                                       kCtaThreads, 0);
+}
+
+cudaError_t launch_fill(void* table, int64_t elems, int dtype, uint64_t seed, float std, cudaStream_t st) {
+  // 65536 * sqrt(4 / 12): standard deviation of the centred sum of four 16-bit fields
+  const float scale = std / 37837.227f;
+  int64_t blocks = (elems + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == 1)
+    eb_fill_kernel<__half><<<(int)blocks, 256, 0, st>>>(static_cast<__half*>(table), elems, seed, scale);
+  else
+    eb_fill_kernel<float><<<(int)blocks, 256, 0, st>>>(static_cast<float*>(table), elems, seed, scale);
+  return cudaGetLastError();
+}
+
+}  // namespace ebk

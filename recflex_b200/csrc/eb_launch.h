@@ -1,0 +1,27 @@
+// Host-callable launchers of the kernels in eb_fused.cuh.  The fused kernel is
+// compiled once per CTAs-per-SM occupancy (its __launch_bounds__ caps the
+// registers accordingly), each in its own translation unit so that the
+// instantiations build in parallel.
+#pragma once
+#include "eb_common.cuh"
+
+namespace ebk {
+
+typedef void (*FusedKernel)(LaunchArgs);
+
+// One definition per occupancy, in eb_fused_inst.cu compiled with -DEB_OCC=<n>.
+FusedKernel fused_kernel_occ1(bool timing);
+FusedKernel fused_kernel_occ2(bool timing);
+FusedKernel fused_kernel_occ3(bool timing);
+FusedKernel fused_kernel_occ4(bool timing);
+FusedKernel fused_kernel_occ5(bool timing);
+FusedKernel fused_kernel_occ6(bool timing);
+FusedKernel fused_kernel_occ7(bool timing);
+FusedKernel fused_kernel_occ8(bool timing);
+
+cudaError_t launch_bind(const LaunchArgs& a, bool zero_feature_times, cudaStream_t st);
+cudaError_t launch_fused(const LaunchArgs& a, int occupancy, bool timing, int grid, cudaStream_t st);
+cudaError_t fused_ctas_per_sm(int occupancy, int* per_sm);
+cudaError_t launch_fill(void* table, int64_t elems, int dtype, uint64_t seed, float std, cudaStream_t st);
+
+}  // namespace ebk

@@ -1,0 +1,432 @@
+// Per-feature schedule templates of the fused embedding-bag kernel (sm_100a).
+//
+// Every schedule works on one *tile* = a run of consecutive bags of one feature,
+// bound to one warp.  A row of the table is read by a *group* of G = 2^lg_group
+// lanes, each lane owning V consecutive elements (one 16-byte load), so a warp
+// holds R = 32 / G row *slots*.  Accumulation is always fp32.
+//
+//   tile_group  (EB_SCHED_GROUP)  slot-per-bag, serial walk, no reduction
+//   tile_warp   (EB_SCHED_WARP)   warp-per-bag, slots split the bag, butterfly reduce
+//   tile_flat   (EB_SCHED_FLAT)   flattened entry stream, segmented reduce at bag boundaries
+//
+// They cover the same ground as the reference's ws:: / onehot:: / obms:: / rbk::
+// device templates (examples/csrc/include/*_kernel.cuh) but share one load/store
+// core, 64-bit row addressing, and write every bag of the tile (empty bags -> 0).
+#pragma once
+#include "eb_common.cuh"
+
+namespace ebk {
+
+constexpr unsigned kFull = 0xffffffffu;
+
+struct TileCtx {
+  const char* table;
+  const char* values;
+  const char* offsets;
+  int64_t rows;
+  int64_t nnz;
+  int64_t batch;
+  float* out;        // already advanced to the feature's first column
+  int64_t out_ld;
+  uint32_t* status;
+  int32_t dim;
+  int32_t row_bytes;
+  int32_t lg_group;
+  int32_t nx;
+  bool idx64;
+  bool has_end;
+  bool out_vec;
+};
+
+__device__ __forceinline__ int64_t load_index(const char* base, int64_t i, bool idx64) {
+  return idx64 ? (int64_t)__ldg(reinterpret_cast<const long long*>(base) + i)
+               : (int64_t)__ldg(reinterpret_cast<const int*>(base) + i);
+}
+
+__device__ __forceinline__ void flag(uint32_t* status, uint32_t bit) {
+  if ((*reinterpret_cast<volatile uint32_t*>(status) & bit) == 0) atomicOr(status, bit);
+}
+
+// ---------------------------------------------------------------------------
+// Row element access: V elements per lane.
+// ---------------------------------------------------------------------------
+template <typename T, int V>
+struct RowOps;
+
+template <>
+struct RowOps<float, 4> {
+  using Raw = uint4;
+  __device__ __forceinline__ static Raw zero() { return make_uint4(0, 0, 0, 0); }
+  __device__ __forceinline__ static Raw load(const char* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+  __device__ __forceinline__ static void add(float (&a)[4], const Raw& r) {
+    a[0] += __uint_as_float(r.x);
+    a[1] += __uint_as_float(r.y);
+    a[2] += __uint_as_float(r.z);
+    a[3] += __uint_as_float(r.w);
+  }
+};
+
+template <>
+struct RowOps<__half, 8> {
+  using Raw = uint4;
+  __device__ __forceinline__ static Raw zero() { return make_uint4(0, 0, 0, 0); }
+  __device__ __forceinline__ static Raw load(const char* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+  __device__ __forceinline__ static void add2(float& x, float& y, unsigned w) {
+    const __half2 h = *reinterpret_cast<const __half2*>(&w);
+    const float2 f = __half22float2(h);
+    x += f.x;
+    y += f.y;
+  }
+  __device__ __forceinline__ static void add(float (&a)[8], const Raw& r) {
+    add2(a[0], a[1], r.x);
+    add2(a[2], a[3], r.y);
+    add2(a[4], a[5], r.z);
+    add2(a[6], a[7], r.w);
+  }
+};
+
+template <>
+struct RowOps<float, 1> {
+  using Raw = float;
+  __device__ __forceinline__ static Raw zero() { return 0.f; }
+  __device__ __forceinline__ static Raw load(const char* p) { return __ldg(reinterpret_cast<const float*>(p)); }
+  __device__ __forceinline__ static void add(float (&a)[1], const Raw& r) { a[0] += r; }
+};
+
+template <>
+struct RowOps<__half, 1> {
+  using Raw = unsigned short;
+  __device__ __forceinline__ static Raw zero() { return 0; }
+  __device__ __forceinline__ static Raw load(const char* p) { return __ldg(reinterpret_cast<const unsigned short*>(p)); }
+  __device__ __forceinline__ static void add(float (&a)[1], const Raw& r) { a[0] += __half2float(__ushort_as_half(r)); }
+};
+
+// Streaming (evict-first) stores: the output is written once and never re-read
+// by this kernel, so it should not displace table rows from L2.
+template <int V>
+__device__ __forceinline__ void store_vals(float* dst, const float (&a)[V], bool vec_ok) {
+  if constexpr (V == 1) {
+    __stcs(dst, a[0]);
+  } else {
+    if (vec_ok) {
+#pragma unroll
+      for (int k = 0; k < V; k += 4)
+        __stcs(reinterpret_cast<float4*>(dst + k), make_float4(a[k], a[k + 1], a[k + 2], a[k + 3]));
+    } else {
+#pragma unroll
+      for (int k = 0; k < V; ++k) __stcs(dst + k, a[k]);
+    }
+  }
+}
+
+template <int V>
+__device__ __forceinline__ void zero_vals(float (&a)[V]) {
+#pragma unroll
+  for (int k = 0; k < V; ++k) a[k] = 0.f;
+}
+
+// ---------------------------------------------------------------------------
+// Bag boundaries of up to 32 consecutive bags, one per lane, relative to the
+// first one.  The sequence is forced to be non-decreasing and inside [0, nnz]
+// (status bit set when that changed anything), so no later step can index
+// outside the feature's index list.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ int64_t raw_offset(const TileCtx& c, int64_t b) {
+  if (!c.has_end && b >= c.batch) return c.nnz;
+  return load_index(c.offsets, b, c.idx64);
+}
+
+__device__ __forceinline__ int64_t clamp_off(int64_t v, int64_t nnz) {
+  return v < 0 ? 0 : (v > nnz ? nnz : v);
+}
+
+struct Chunk {
+  int64_t e0;  // absolute position of the chunk's first entry
+  int lo, hi;  // this lane's bag: entries [lo, hi) relative to e0 (lo == hi == n for lanes past the chunk)
+  int n;       // entries in the chunk
+};
+
+__device__ __forceinline__ Chunk load_chunk(const TileCtx& c, int64_t bb, int nb, int lane) {
+  const int li = lane <= nb ? lane : nb;
+  const int64_t a_raw = raw_offset(c, bb + li);
+  int64_t end_raw = __shfl_sync(kFull, a_raw, 31);
+  if (nb == 32) end_raw = raw_offset(c, bb + 32);
+  int64_t m = clamp_off(a_raw, c.nnz);
+  int64_t endm = clamp_off(end_raw, c.nnz);
+  bool bad = (m != a_raw) || (endm != end_raw);
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int64_t t = __shfl_up_sync(kFull, m, d);
+    if (lane >= d && t > m) { m = t; bad = true; }
+  }
+  const int64_t m31 = __shfl_sync(kFull, m, 31);
+  if (m31 > endm) { endm = m31; bad = true; }
+  Chunk ch;
+  ch.e0 = __shfl_sync(kFull, m, 0);
+  int64_t nxt = __shfl_down_sync(kFull, m, 1);
+  if (lane == 31) nxt = endm;
+  int64_t total = endm - ch.e0;
+  if (total > 0x3fffffff) { total = 0x3fffffff; bad = true; }  // more than 2^30 indices in 32 bags: refuse the excess
+  int64_t lo = m - ch.e0, hi = nxt - ch.e0;
+  if (lo > total) lo = total;
+  if (hi > total) hi = total;
+  ch.lo = (int)lo;
+  ch.hi = (int)hi;
+  ch.n = (int)total;
+  if (__any_sync(kFull, bad) && lane == 0) flag(c.status, kStatusBadOffsets);
+  return ch;
+}
+
+// Fetch U rows for positions p[u] of the chunk-relative entry list.
+template <typename T, int V, int U>
+__device__ __forceinline__ void fetch_rows(const TileCtx& c, const char* vals, const char* tcol,
+                                           const int (&p)[U], const bool (&ok)[U],
+                                           typename RowOps<T, V>::Raw (&rows)[U]) {
+  using Ops = RowOps<T, V>;
+  int64_t idx[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) idx[u] = ok[u] ? load_index(vals, p[u], c.idx64) : 0;
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    rows[u] = Ops::zero();
+    if (ok[u]) {
+      if ((uint64_t)idx[u] < (uint64_t)c.rows)
+        rows[u] = Ops::load(tcol + idx[u] * (int64_t)c.row_bytes);
+      else
+        flag(c.status, kStatusBadIndex);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// EB_SCHED_GROUP: each slot owns one bag at a time and walks it serially.
+// ---------------------------------------------------------------------------
+template <typename T, int V, int U>
+__device__ __forceinline__ void tile_group(const TileCtx& c, int64_t b0, int64_t b1, int lane) {
+  using Ops = RowOps<T, V>;
+  const int lgG = c.lg_group, G = 1 << lgG, R = 32 >> lgG;
+  const int r = lane >> lgG, cl = lane & (G - 1);
+  for (int xc = 0; xc < c.nx; ++xc) {
+    const int cs = (xc * G + cl) * V;
+    const bool col_ok = cs < c.dim;
+    const char* tcol = c.table + (size_t)cs * sizeof(T);
+    float* ocol = c.out + cs;
+    for (int64_t bb = b0; bb < b1; bb += 32) {
+      const int nb = (int)((b1 - bb) < 32 ? (b1 - bb) : 32);
+      const Chunk ch = load_chunk(c, bb, nb, lane);
+      const char* vals = c.values + ch.e0 * (c.idx64 ? 8 : 4);
+      for (int i0 = 0; i0 < nb; i0 += R) {
+        const int bi = i0 + r;
+        const int s = __shfl_sync(kFull, ch.lo, bi & 31);
+        const int e = __shfl_sync(kFull, ch.hi, bi & 31);
+        const int len = bi < nb ? e - s : 0;
+        const int maxlen = __reduce_max_sync(kFull, len);
+        float acc[V];
+        zero_vals<V>(acc);
+        for (int q = 0; q < maxlen; q += U) {
+          int p[U];
+          bool ok[U];
+          typename Ops::Raw rows[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            p[u] = s + q + u;
+            ok[u] = col_ok && (q + u < len);
+          }
+          fetch_rows<T, V, U>(c, vals, tcol, p, ok, rows);
+#pragma unroll
+          for (int u = 0; u < U; ++u) Ops::add(acc, rows[u]);
+        }
+        if (bi < nb && col_ok) store_vals<V>(ocol + (bb + bi) * c.out_ld, acc, c.out_vec);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// EB_SCHED_WARP: the warp owns one bag at a time; its R slots split the bag.
+// ---------------------------------------------------------------------------
+template <typename T, int V, int U>
+__device__ __forceinline__ void tile_warp(const TileCtx& c, int64_t b0, int64_t b1, int lane) {
+  using Ops = RowOps<T, V>;
+  const int lgG = c.lg_group, G = 1 << lgG, R = 32 >> lgG;
+  const int r = lane >> lgG, cl = lane & (G - 1);
+  for (int xc = 0; xc < c.nx; ++xc) {
+    const int cs = (xc * G + cl) * V;
+    const bool col_ok = cs < c.dim;
+    const char* tcol = c.table + (size_t)cs * sizeof(T);
+    float* ocol = c.out + cs;
+    for (int64_t bb = b0; bb < b1; bb += 32) {
+      const int nb = (int)((b1 - bb) < 32 ? (b1 - bb) : 32);
+      const Chunk ch = load_chunk(c, bb, nb, lane);
+      const char* vals = c.values + ch.e0 * (c.idx64 ? 8 : 4);
+      for (int i = 0; i < nb; ++i) {
+        const int s = __shfl_sync(kFull, ch.lo, i);
+        const int e = __shfl_sync(kFull, ch.hi, i);
+        float acc[V];
+        zero_vals<V>(acc);
+        for (int q = s; q < e; q += R * U) {
+          int p[U];
+          bool ok[U];
+          typename Ops::Raw rows[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            p[u] = q + u * R + r;
+            ok[u] = col_ok && p[u] < e;
+          }
+          fetch_rows<T, V, U>(c, vals, tcol, p, ok, rows);
+#pragma unroll
+          for (int u = 0; u < U; ++u) Ops::add(acc, rows[u]);
+        }
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          if (d >= G) {
+#pragma unroll
+            for (int k = 0; k < V; ++k) acc[k] += __shfl_xor_sync(kFull, acc[k], d);
+          }
+        }
+        if (r == 0 && col_ok) store_vals<V>(ocol + (bb + i) * c.out_ld, acc, c.out_vec);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// EB_SCHED_FLAT: the warp streams the chunk's entries R at a time ("steps"),
+// U steps in flight, whatever the bag lengths.  Slot r of step j holds entry
+// j + r.  While a step lies strictly inside the open bag W every slot just
+// accumulates.  A step that touches a boundary closes W (butterfly over the
+// slots' partial sums), reduces the bags that start inside the step with a
+// segmented shuffle reduction, stores the ones that also end there, and keeps
+// the last one as the new open bag.
+// ---------------------------------------------------------------------------
+template <typename T, int V, int U>
+__device__ __forceinline__ void tile_flat(const TileCtx& c, int64_t b0, int64_t b1, int lane) {
+  using Ops = RowOps<T, V>;
+  const int lgG = c.lg_group, G = 1 << lgG, R = 32 >> lgG;
+  const int r = lane >> lgG, cl = lane & (G - 1);
+  for (int xc = 0; xc < c.nx; ++xc) {
+    const int cs = (xc * G + cl) * V;
+    const bool col_ok = cs < c.dim;
+    const char* tcol = c.table + (size_t)cs * sizeof(T);
+    float* ocol = c.out + cs;
+    for (int64_t bb = b0; bb < b1; bb += 32) {
+      const int nb = (int)((b1 - bb) < 32 ? (b1 - bb) : 32);
+      const Chunk ch = load_chunk(c, bb, nb, lane);
+      const char* vals = c.values + ch.e0 * (c.idx64 ? 8 : 4);
+      const int n = ch.n;
+      const bool nonempty = ch.hi > ch.lo;
+      float* orow = ocol + bb * c.out_ld;
+
+      // empty bags pool to zero
+      {
+        const unsigned valid = nb == 32 ? kFull : ((1u << nb) - 1u);
+        unsigned em = ~__ballot_sync(kFull, nonempty) & valid;
+        float z[V];
+        zero_vals<V>(z);
+        while (em) {
+          // slot r takes the r-th remaining empty bag
+          const int i = (int)__fns(em, 0, r + 1);  // -1 when fewer than r + 1 remain
+          if (i >= 0 && col_ok) store_vals<V>(orow + (int64_t)i * c.out_ld, z, c.out_vec);
+          // drop the R lowest set bits
+          for (int k = 0; k < R && em; ++k) em &= em - 1;
+        }
+      }
+
+      int wbag = -1;  // open bag (chunk-local), -1 = none
+      int endw = 0;   // its end; when none, a position <= the next step so that the step takes the boundary path
+      float acc[V];
+      zero_vals<V>(acc);
+
+      for (int base = 0; base < n; base += R * U) {
+        int p[U];
+        bool ok[U];
+        typename Ops::Raw rows[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          p[u] = base + u * R + r;
+          ok[u] = col_ok && p[u] < n;
+        }
+        fetch_rows<T, V, U>(c, vals, tcol, p, ok, rows);
+
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int j = base + u * R;
+          if (j < n) {
+            if (j + R < endw) {
+              Ops::add(acc, rows[u]);
+            } else {
+              const int pj = j + r;
+              const bool inw = pj < endw;  // false everywhere when no bag is open
+              float x[V];
+              zero_vals<V>(x);
+              if (wbag >= 0) {
+                if (inw) Ops::add(acc, rows[u]);
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                  if (d >= G) {
+#pragma unroll
+                    for (int k = 0; k < V; ++k) acc[k] += __shfl_xor_sync(kFull, acc[k], d);
+                  }
+                }
+                if (r == 0 && col_ok) store_vals<V>(orow + (int64_t)wbag * c.out_ld, acc, c.out_vec);
+              }
+              if (!inw) Ops::add(x, rows[u]);
+
+              // bags that start inside [j, j + R): one head bit per slot
+              const bool head_here = nonempty && ch.lo >= j && ch.lo < j + R;
+              const unsigned head_mask = __reduce_or_sync(kFull, head_here ? (1u << (ch.lo - j)) : 0u);
+              if (head_mask == 0u) {
+                wbag = -1;
+                endw = j + R;
+                zero_vals<V>(acc);
+              } else {
+                const unsigned m_before = __ballot_sync(kFull, nonempty && ch.lo < j);
+                const unsigned m_upto = __ballot_sync(kFull, nonempty && ch.lo < j + R);
+                const unsigned head_bags = m_upto & ~m_before;
+                const int lastbag = 31 - __clz(m_upto);
+                const int last_end = __shfl_sync(kFull, ch.hi, lastbag);
+                const bool last_cont = last_end > j + R;
+                const int last_head = 31 - __clz(head_mask);
+
+                const unsigned below = head_mask & ((2u << r) - 1u);
+                const bool has_seg = below != 0u;
+                const int seg_start = 31 - __clz(below);
+                const unsigned above = r == 31 ? 0u : (head_mask >> (r + 1));
+                const int seg_end = above ? (r + __ffs(above) - 1) : (R - 1);
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                  if (d < R) {
+                    const bool take = has_seg && (r + d <= seg_end);
+#pragma unroll
+                    for (int k = 0; k < V; ++k) {
+                      const float y = __shfl_down_sync(kFull, x[k], d << lgG);
+                      if (take) x[k] += y;
+                    }
+                  }
+                }
+                const bool is_head = has_seg && r == seg_start;
+                const bool keeps = is_head && seg_start == last_head && last_cont;
+                if (is_head && !keeps && col_ok) {
+                  const int q = __popc(head_mask & ((1u << r) - 1u));
+                  const int mybag = __fns(head_bags, 0, q + 1);
+                  store_vals<V>(orow + (int64_t)mybag * c.out_ld, x, c.out_vec);
+                }
+#pragma unroll
+                for (int k = 0; k < V; ++k) acc[k] = keeps ? x[k] : 0.f;
+                if (last_cont) {
+                  wbag = lastbag;
+                  endw = last_end;
+                } else {
+                  wbag = -1;
+                  endw = j + R;
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+}
+
+}  // namespace ebk

@@ -1,0 +1,353 @@
+"""PyTorch modules with the interface of RecFlex's `RecFlex/rec_modules.py`.
+
+`FeatEmbed` owns the embedding tables and runs the fused multi-feature
+embedding-bag forward (sum pooling, outputs of all features concatenated into
+one `[batch, sum(dim_f)]` fp32 tensor) through the C ABI of
+librecflex_b200.so.  `FeatPreprocess` turns the reference's text input (one
+string of comma-separated indices per sample and feature) into per-feature
+`values` / `offsets` tensors, and `FeatProcessEmbed` composes the two exactly
+like the reference's class of the same name (rec_modules.py:114-140).
+
+PyTorch is used for device memory, streams and module plumbing only; there is
+no PyTorch or CPU implementation of the forward behind these classes.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from concurrent.futures import ThreadPoolExecutor
+from types import ModuleType
+from typing import List, Optional, Sequence, Tuple, Union
+
+import numpy as np
+import torch
+import torch.nn as nn
+
+from . import _lib
+from ._lib import EbSchedule
+
+
+def _device_index(device) -> int:
+    dev = torch.device(device) if not isinstance(device, int) else torch.device("cuda", device)
+    if dev.type != "cuda":
+        raise ValueError(f"FeatEmbed needs a CUDA device, got {dev}")
+    return dev.index if dev.index is not None else torch.cuda.current_device()
+
+
+class Schedule:
+    """One feature's schedule: kind ('auto' | 'group' | 'warp' | 'flat'), unroll, bags_per_tile.
+
+    The counterpart of the reference's (ScheduleBase subclass, params NamedTuple)
+    pair (code_emitter/schedule_base.py:54-87); see include/recflex_b200.h for
+    what each kind does.
+    """
+
+    __slots__ = ("kind", "unroll", "bags_per_tile")
+
+    def __init__(self, kind: Union[str, int] = "auto", unroll: int = 0, bags_per_tile: int = 0):
+        self.kind = _lib.SCHED_KINDS[kind] if isinstance(kind, str) else int(kind)
+        self.unroll = int(unroll)
+        self.bags_per_tile = int(bags_per_tile)
+
+    def to_c(self) -> EbSchedule:
+        return EbSchedule(self.kind, self.unroll, 0, self.bags_per_tile)
+
+    def to_json(self) -> dict:
+        return {"kind": _lib.SCHED_NAMES[self.kind], "unroll": self.unroll, "bags_per_tile": self.bags_per_tile}
+
+    @staticmethod
+    def from_json(d: dict) -> "Schedule":
+        return Schedule(d["kind"], d.get("unroll", 0), d.get("bags_per_tile", 0))
+
+    def __repr__(self) -> str:
+        return f"Schedule({_lib.SCHED_NAMES[self.kind]!r}, unroll={self.unroll}, bags_per_tile={self.bags_per_tile})"
+
+    def __eq__(self, other) -> bool:
+        return isinstance(other, Schedule) and (self.kind, self.unroll, self.bags_per_tile) == (
+            other.kind, other.unroll, other.bags_per_tile)
+
+
+class FeatEmbed(nn.Module):
+    """Fused embedding-bag forward over a list of tables (rec_modules.py:57-111 in the reference).
+
+    Parameters mirror the reference: either `embed_tables` (a list of
+    `[rows, dim]` CUDA tensors, fp32 or fp16, which the module keeps alive and
+    whose storage must not move) or `table_shapes` (a list of `(rows, dim)`;
+    tables are then created with `torch.randn` in `dtype`).
+    """
+
+    def __init__(self, device, embed_tables: Optional[List[torch.Tensor]] = None,
+                 table_shapes: Optional[Sequence[Tuple[int, int]]] = None, dtype: torch.dtype = torch.float32):
+        super().__init__()
+        self._h = C.c_void_p()
+        self._lib = _lib.load()  # raises when the CUDA library is missing: there is no fallback
+        self.device = torch.device("cuda", _device_index(device))
+        if embed_tables:
+            self.embed_tables = list(embed_tables)
+        elif table_shapes:
+            self.embed_tables = [torch.randn(tuple(s), dtype=dtype, device=self.device) for s in table_shapes]
+        else:
+            raise Exception("At least one of embed_tables and table_shapes should be given!")
+        F = len(self.embed_tables)
+        rows = (C.c_int64 * F)()
+        dims = (C.c_int32 * F)()
+        dtypes = (C.c_int32 * F)()
+        ptrs = (C.c_void_p * F)()
+        for f, t in enumerate(self.embed_tables):
+            if t.dim() != 2 or not t.is_cuda or t.device != self.device or not t.is_contiguous():
+                raise ValueError(f"table {f} must be a contiguous 2-D tensor on {self.device}")
+            if t.dtype not in (torch.float32, torch.float16):
+                raise ValueError(f"table {f}: dtype {t.dtype} is not supported (float32 or float16)")
+            rows[f], dims[f] = t.shape[0], t.shape[1]
+            dtypes[f] = _lib.EB_F32 if t.dtype == torch.float32 else _lib.EB_F16
+            ptrs[f] = t.data_ptr()
+        _lib.check(self._lib.eb_create(C.byref(self._h), self.device.index, F, rows, dims, dtypes, ptrs))
+        # raw device pointers, as the reference keeps them (rec_modules.py:70)
+        self.embed_table_ptrs = torch.tensor([t.data_ptr() for t in self.embed_tables], dtype=torch.int64)
+        self.num_features = F
+        self.output_units = sum(int(t.shape[1]) for t in self.embed_tables)
+        ws = C.c_size_t()
+        _lib.check(self._lib.eb_workspace_bytes(self._h, C.byref(ws)))
+        self._ws_bytes = int(ws.value)
+        self._ws = torch.empty(self._ws_bytes + 128, dtype=torch.uint8, device=self.device)
+        self._ws_ptr = (self._ws.data_ptr() + 127) // 128 * 128
+        self._staging = None
+        self._staging_ptr = 0
+        self._staging_bytes = 0
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h is not None and h.value:
+            self._lib.eb_destroy(h)
+            self._h = C.c_void_p()
+
+    # -- schedules ---------------------------------------------------------
+    @property
+    def max_concurrent_blocks(self) -> int:
+        """Persistent CTAs of the fused kernel (reference: torch.ops.recom.get_max_concurrent_blocks)."""
+        n = C.c_int()
+        _lib.check(self._lib.eb_max_concurrent_ctas(self._h, 0, C.byref(n)))
+        return int(n.value)
+
+    def set_schedules(self, schedules: Optional[Sequence[Schedule]] = None, occupancy: int = 0) -> None:
+        arr = None
+        if schedules is not None:
+            if len(schedules) != self.num_features:
+                raise ValueError(f"{len(schedules)} schedules for {self.num_features} features")
+            arr = (EbSchedule * self.num_features)(*[s.to_c() for s in schedules])
+        _lib.check(self._lib.eb_set_schedules(self._h, arr, int(occupancy)))
+
+    def get_schedules(self) -> Tuple[List[Schedule], int]:
+        arr = (EbSchedule * self.num_features)()
+        occ = C.c_int()
+        _lib.check(self._lib.eb_get_schedules(self._h, arr, C.byref(occ)))
+        return [Schedule(s.kind, s.unroll, s.bags_per_tile) for s in arr], int(occ.value)
+
+    # -- forward -----------------------------------------------------------
+    def _stream(self) -> C.c_void_p:
+        return C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    @staticmethod
+    def _index_dtype(t: torch.Tensor) -> int:
+        if t.dtype == torch.int32:
+            return _lib.EB_I32
+        if t.dtype == torch.int64:
+            return _lib.EB_I64
+        raise TypeError(f"values/offsets must be int32 or int64, got {t.dtype}")
+
+    def forward(self, values: Sequence[torch.Tensor], offsets: Sequence[torch.Tensor],
+                include_last_offset: bool = True, timing: bool = False, timing_schedules: Optional[int] = None,
+                out: Optional[torch.Tensor] = None):
+        """Pool every feature's bags and concatenate: returns fp32 `[batch, output_units]`.
+
+        values[f]: 1-D int32/int64 indices into table f; offsets[f]: bag starts,
+        `batch + 1` entries ending with `len(values[f])` (the reference's device
+        format) or `batch` entries with `include_last_offset=False` (the
+        torch.nn.EmbeddingBag default).  With `timing=True` returns
+        `(output, per_feature_times)` like the reference (rec_modules.py:96-109):
+        a float64 tensor of summed per-tile device time in milliseconds for the
+        first `timing_schedules` features.
+        """
+        F = self.num_features
+        if len(values) != F or len(offsets) != F:
+            raise ValueError(f"expected {F} values and offsets tensors, got {len(values)} and {len(offsets)}")
+        idt = self._index_dtype(values[0])
+        n_off = offsets[0].numel()
+        batch = n_off - 1 if include_last_offset else n_off
+        if batch < 0:
+            raise ValueError("offsets with include_last_offset=True need at least one entry")
+        vp = (C.c_void_p * F)()
+        op = (C.c_void_p * F)()
+        nnz = (C.c_int64 * F)()
+        keep = []
+        for f in range(F):
+            v, o = values[f], offsets[f]
+            if self._index_dtype(v) != idt or self._index_dtype(o) != idt:
+                raise TypeError("all values and offsets tensors must share one integer dtype")
+            if o.numel() != n_off:
+                raise ValueError(f"feature {f}: offsets has {o.numel()} entries, feature 0 has {n_off}")
+            if v.device != self.device or o.device != self.device:
+                raise ValueError(f"feature {f}: values/offsets must live on {self.device}")
+            if not v.is_contiguous():
+                v = v.contiguous()
+            if not o.is_contiguous():
+                o = o.contiguous()
+            keep.append((v, o))
+            vp[f], op[f], nnz[f] = v.data_ptr(), o.data_ptr(), v.numel()
+        if out is None:
+            out = torch.empty((batch, self.output_units), dtype=torch.float32, device=self.device)
+        elif out.dtype != torch.float32 or out.dim() != 2 or out.shape[0] != batch or out.stride(1) != 1 \
+                or out.shape[1] < self.output_units:
+            raise ValueError("out must be an fp32 [batch, >= output_units] tensor with unit column stride")
+        ld = out.stride(0) if batch > 1 else max(out.shape[1], self.output_units)
+        if not timing:
+            _lib.check(self._lib.eb_forward(self._h, batch, vp, op, nnz, idt, int(include_last_offset),
+                                            C.c_void_p(out.data_ptr()), ld, C.c_void_p(self._ws_ptr),
+                                            self._ws_bytes, self._stream()))
+            return out
+        ns = (C.c_double * F)()
+        _lib.check(self._lib.eb_forward_timed(self._h, batch, vp, op, nnz, idt, int(include_last_offset),
+                                              C.c_void_p(out.data_ptr()), ld, C.c_void_p(self._ws_ptr),
+                                              self._ws_bytes, self._stream(), ns))
+        n_t = F if not timing_schedules or timing_schedules > F else timing_schedules
+        times = torch.tensor([ns[f] * 1e-6 for f in range(n_t)], dtype=torch.float64)
+        return out, times
+
+    def forward_packed(self, values: torch.Tensor, offsets: torch.Tensor, out: Optional[torch.Tensor] = None):
+        """Same forward for one packed batch: `values` = all features' indices back to back,
+        `offsets` = `[num_features, batch + 1]`, both on the device."""
+        if offsets.dim() != 2 or offsets.shape[0] != self.num_features or not offsets.is_contiguous():
+            raise ValueError("offsets must be a contiguous [num_features, batch + 1] tensor")
+        idt = self._index_dtype(values)
+        if self._index_dtype(offsets) != idt:
+            raise TypeError("values and offsets must share one integer dtype")
+        batch = offsets.shape[1] - 1
+        if out is None:
+            out = torch.empty((batch, self.output_units), dtype=torch.float32, device=self.device)
+        ld = out.stride(0) if batch > 1 else max(out.shape[1], self.output_units)
+        _lib.check(self._lib.eb_forward_packed(self._h, batch, C.c_void_p(values.data_ptr()),
+                                               C.c_void_p(offsets.data_ptr()), idt, C.c_void_p(out.data_ptr()), ld,
+                                               C.c_void_p(self._ws_ptr), self._ws_bytes, self._stream()))
+        return out
+
+    def forward_host(self, values: torch.Tensor, offsets: torch.Tensor, out: Optional[torch.Tensor] = None):
+        """End-to-end call on HOST tensors (pinned for full copy speed): uploads the packed batch,
+        runs the forward and downloads the `[batch, output_units]` result into `out` (a host
+        tensor, allocated pinned when omitted).  Returns after enqueueing on the current stream."""
+        if values.is_cuda or offsets.is_cuda:
+            raise ValueError("forward_host takes host tensors")
+        idt = self._index_dtype(values)
+        batch = offsets.shape[1] - 1
+        if out is None:
+            out = torch.empty((batch, self.output_units), dtype=torch.float32, pin_memory=True)
+        need = C.c_size_t()
+        _lib.check(self._lib.eb_host_staging_bytes(self._h, batch, values.numel(), idt, C.byref(need)))
+        if self._staging_bytes < need.value:
+            self._staging = torch.empty(int(need.value) + 256, dtype=torch.uint8, device=self.device)
+            self._staging_ptr = (self._staging.data_ptr() + 255) // 256 * 256
+            self._staging_bytes = int(need.value)
+        _lib.check(self._lib.eb_forward_host(self._h, batch, C.c_void_p(values.data_ptr()), values.numel(),
+                                             C.c_void_p(offsets.data_ptr()), idt, C.c_void_p(out.data_ptr()),
+                                             C.c_void_p(self._staging_ptr), self._staging_bytes,
+                                             C.c_void_p(self._ws_ptr), self._ws_bytes, self._stream()))
+        return out
+
+    def kernel_timing(self, enable: bool = True) -> None:
+        """Record a CUDA event pair around every fused-kernel launch from now on (ring of 256)."""
+        _lib.check(self._lib.eb_kernel_timing(self._h, int(enable)))
+
+    def kernel_times(self) -> List[float]:
+        """Milliseconds of each fused-kernel launch since the last read (synchronises on them)."""
+        buf = (C.c_float * 256)()
+        n = C.c_int()
+        _lib.check(self._lib.eb_kernel_times(self._h, buf, 256, C.byref(n)))
+        return [float(buf[i]) for i in range(n.value)]
+
+    def check_status(self) -> None:
+        """Raise if the last forward met an out-of-range index or non-monotone offsets (synchronises)."""
+        _lib.check(self._lib.eb_check_status(self._h, C.c_void_p(self._ws_ptr), self._stream()))
+
+
+def parse_bags(lines: Sequence[str]) -> Tuple[np.ndarray, np.ndarray]:
+    """One feature's text batch -> (values int32, offsets int32 [batch + 1]) with the reference's
+    parsing rules (examples/csrc/warp_per_sample_preprocess.cu:6-38): every non-digit character
+    ends a number, an empty string is an empty bag."""
+    lib = _lib.load()
+    text = "\n".join(lines).encode()
+    batch = len(lines)
+    cap = len(text) + 1
+    values = np.empty(cap, dtype=np.int32)
+    offsets = np.empty(batch + 1, dtype=np.int32)
+    nnz = C.c_int64()
+    _lib.check(lib.eb_parse_bags(text, len(text), batch, values.ctypes.data_as(C.c_void_p), cap,
+                                 offsets.ctypes.data_as(C.c_void_p), C.byref(nnz)))
+    return values[: nnz.value].copy(), offsets
+
+
+class FeatPreprocess(nn.Module):
+    """Text batch -> device tensors (reference: rec_modules.py:19-54).
+
+    `recom_host` is accepted for signature compatibility and ignored: the
+    parser lives in librecflex_b200.so and tiling / block binding happen on the
+    device inside the forward.
+    """
+
+    def __init__(self, recom_host: Optional[ModuleType], device):
+        super().__init__()
+        self.recom_host = recom_host
+        self.device = torch.device("cuda", _device_index(device))
+        self._pool = ThreadPoolExecutor(max_workers=8)
+
+    def forward(self, raw_data: List[List[str]], max_concurrent_blocks: int = 0):
+        parsed = list(self._pool.map(parse_bags, raw_data))  # ctypes releases the GIL: features parse in parallel
+        values = [torch.from_numpy(v).to(self.device, non_blocking=True) for v, _ in parsed]
+        offsets = [torch.from_numpy(o).to(self.device, non_blocking=True) for _, o in parsed]
+        return values, offsets
+
+
+class FeatProcessEmbed(nn.Module):
+    """Preprocess + embed (reference: rec_modules.py:114-140), same constructor and forward arguments."""
+
+    def __init__(self, recom_host: Optional[ModuleType] = None, device=None,
+                 embed_tables: Optional[List[torch.Tensor]] = None,
+                 table_shapes: Optional[Sequence[Tuple[int, int]]] = None, librecom_path: Optional[str] = None):
+        super().__init__()
+        if device is None:
+            device = torch.cuda.current_device()
+        self.device = torch.device("cuda", _device_index(device))
+        self.preprocess_layer = FeatPreprocess(recom_host, device=self.device)
+        self.embed_layer = FeatEmbed(device=self.device, embed_tables=embed_tables, table_shapes=table_shapes)
+        self.max_concurrent_blocks = self.embed_layer.max_concurrent_blocks
+
+    def forward(self, raw_data: List[List[str]], timing: bool = False, timing_schedules: Optional[int] = None,
+                timing_kernel: bool = False):
+        values, offsets = self.preprocess_layer(raw_data, self.max_concurrent_blocks)
+        if not timing_kernel:
+            return self.embed_layer(values, offsets, timing=timing, timing_schedules=timing_schedules)
+        start = torch.cuda.Event(enable_timing=True)
+        end = torch.cuda.Event(enable_timing=True)
+        start.record()
+        result = self.embed_layer(values, offsets, timing=timing, timing_schedules=timing_schedules)
+        end.record()
+        end.synchronize()
+        return result, start.elapsed_time(end)
+
+
+class RecomModel(nn.Module):
+    """Fused embedding + MLP (reference: rec_modules.py:143-179): embed -> [batch, output_units] -> MLP -> sigmoid."""
+
+    def __init__(self, mlp_unit_nums: List[int], device, embed_tables: Optional[List[torch.Tensor]] = None,
+                 table_shapes: Optional[Sequence[Tuple[int, int]]] = None):
+        super().__init__()
+        self.device = torch.device("cuda", _device_index(device))
+        self.embed_layer = FeatEmbed(device=self.device, embed_tables=embed_tables, table_shapes=table_shapes)
+        layers = []
+        unit_nums = [self.embed_layer.output_units] + list(mlp_unit_nums) + [1]
+        for i in range(len(unit_nums) - 1):
+            layers.append(nn.Linear(unit_nums[i], unit_nums[i + 1], bias=True, device=self.device))
+            layers.append(nn.Sigmoid() if i + 2 == len(unit_nums) else nn.ReLU())
+        self.mlp = nn.Sequential(*layers)
+
+    def forward(self, values: Sequence[torch.Tensor], offsets: Sequence[torch.Tensor],
+                include_last_offset: bool = True):
+        embed_output = self.embed_layer(values, offsets, include_last_offset=include_last_offset)
+        return self.mlp(embed_output)

@@ -1,0 +1,203 @@
+"""GPU parity: the fused CUDA forward (through the C ABI) against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+from recflex_b200 import synth
+from recflex_b200.rec_modules import FeatEmbed, Schedule
+from tests.helpers import (TOL, all_schedules, check_against_oracle, device_tables, small_model, to_device)
+
+pytestmark = pytest.mark.gpu
+
+KINDS = ["group", "warp", "flat"]
+UNROLLS = [1, 2, 4, 8]
+
+
+@pytest.fixture(scope="module")
+def cfg1():
+    cfg, tables, values, offsets = small_model(1, 1.0, 256)
+    return cfg, tables, values, offsets, FeatEmbed("cuda:0", embed_tables=device_tables(tables))
+
+
+@pytest.mark.parametrize("kind", KINDS)
+@pytest.mark.parametrize("unroll", UNROLLS)
+def test_cfg1_every_schedule(cfg1, kind, unroll):
+    cfg, tables, values, offsets, mod = cfg1
+    mod.set_schedules(all_schedules(kind, unroll, len(tables)), occupancy=4)
+    out = mod(to_device(values), to_device(offsets))
+    mod.check_status()
+    check_against_oracle(out, tables, values, offsets, "f32")
+
+
+@pytest.mark.parametrize("occupancy", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_cfg1_every_occupancy(cfg1, occupancy):
+    cfg, tables, values, offsets, mod = cfg1
+    mod.set_schedules(all_schedules("flat", 4, len(tables)), occupancy=occupancy)
+    assert mod.max_concurrent_blocks == occupancy * torch.cuda.get_device_properties(0).multi_processor_count
+    out = mod(to_device(values), to_device(offsets))
+    check_against_oracle(out, tables, values, offsets, "f32")
+
+
+def test_cfg1_matches_torch_embedding_bag(cfg1):
+    cfg, tables, values, offsets, mod = cfg1
+    mod.set_schedules(all_schedules("auto", 0, len(tables)), occupancy=4)
+    out = mod(to_device(values), to_device(offsets)).cpu()
+    ref = oracle.pool_torch(tables, values, offsets)
+    torch.testing.assert_close(out, ref, **TOL["f32"])
+
+
+@pytest.mark.parametrize("kind", KINDS)
+@pytest.mark.parametrize("cfg_id,scale,batch,tag", [(2, 0.01, 1000, "f32"), (3, 2e-4, 777, "f16"), (5, 0.01, 600, "f32"),
+                                                    (4, 1e-4, 300, "f16")])
+def test_scaled_configs(kind, cfg_id, scale, batch, tag):
+    cfg, tables, values, offsets = small_model(cfg_id, scale, batch)
+    mod = FeatEmbed("cuda:0", embed_tables=device_tables(tables))
+    for unroll in (2, 8):
+        mod.set_schedules(all_schedules(kind, unroll, len(tables)))
+        out = mod(to_device(values), to_device(offsets))
+        mod.check_status()
+        check_against_oracle(out, tables, values, offsets, tag)
+
+
+def test_int64_indices_and_offsets_without_end(cfg1):
+    cfg, tables, values, offsets, mod = cfg1
+    mod.set_schedules(all_schedules("flat", 4, len(tables)))
+    v64 = to_device(values, dtype=np.int64)
+    o64 = to_device(offsets, dtype=np.int64)
+    out = mod(v64, o64)
+    check_against_oracle(out, tables, values, offsets, "f32")
+    out2 = mod(v64, [o[:-1].contiguous() for o in o64], include_last_offset=False)
+    assert torch.equal(out, out2)
+    out3 = mod(to_device(values), [o[:-1].contiguous() for o in to_device(offsets)], include_last_offset=False)
+    assert torch.equal(out, out3)
+
+
+def test_packed_and_host_paths(cfg1):
+    cfg, tables, values, offsets, mod = cfg1
+    mod.set_schedules(all_schedules("flat", 4, len(tables)))
+    ref = mod(to_device(values), to_device(offsets))
+    pv, po = synth.pack_batch(values, offsets)
+    out = mod.forward_packed(torch.from_numpy(pv).cuda(), torch.from_numpy(po).cuda())
+    assert torch.equal(out, ref)
+    hv = torch.from_numpy(pv).pin_memory()
+    ho = torch.from_numpy(po).pin_memory()
+    hout = mod.forward_host(hv, ho)
+    torch.cuda.synchronize()
+    assert torch.equal(hout, ref.cpu())
+
+
+@pytest.mark.parametrize("kind", KINDS)
+def test_ragged_edges(kind):
+    """Empty bags, all-empty features, one giant bag, batch sizes around the 32-bag chunk."""
+    rng = np.random.default_rng(5)
+    dims = [4, 8, 12, 20, 32, 64, 128, 256, 3, 7, 100]
+    dts = [np.float32, np.float16]
+    for batch in (1, 31, 32, 33, 95):
+        tables, values, offsets = [], [], []
+        for i, d in enumerate(dims):
+            rows = 50 + 13 * i
+            tables.append((rng.standard_normal((rows, d)) * 0.1).astype(dts[i % 2]))
+            mode = i % 4
+            if mode == 0:
+                lens = rng.integers(0, 3, batch)
+            elif mode == 1:
+                lens = np.zeros(batch, dtype=np.int64)
+            elif mode == 2:
+                lens = np.zeros(batch, dtype=np.int64)
+                lens[batch // 2] = 700
+            else:
+                lens = rng.integers(0, 70, batch)
+            o = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+            offsets.append(o)
+            values.append(rng.integers(0, rows, o[-1]).astype(np.int32))
+        mod = FeatEmbed("cuda:0", embed_tables=device_tables(tables))
+        for unroll in (1, 4):
+            mod.set_schedules(all_schedules(kind, unroll, len(dims)))
+            out = mod(to_device(values), to_device(offsets))
+            mod.check_status()
+            expect = oracle.pool(tables, values, offsets, acc64=True)
+            np.testing.assert_allclose(out.cpu().numpy(), expect, rtol=2e-3, atol=1e-5)
+
+
+def test_output_slice_with_wider_leading_dimension(cfg1):
+    cfg, tables, values, offsets, mod = cfg1
+    mod.set_schedules(all_schedules("flat", 4, len(tables)))
+    ref = mod(to_device(values), to_device(offsets))
+    wide = torch.full((ref.shape[0], ref.shape[1] + 37), -7.0, device="cuda:0")
+    out = mod(to_device(values), to_device(offsets), out=wide)
+    assert torch.equal(out[:, : ref.shape[1]], ref)
+    assert torch.all(out[:, ref.shape[1]:] == -7.0)
+
+
+def test_bad_inputs_are_flagged_not_dereferenced(cfg1):
+    cfg, tables, values, offsets, mod = cfg1
+    from recflex_b200._lib import EbError
+
+    mod.set_schedules(all_schedules("flat", 4, len(tables)))
+    bad = [v.copy() for v in values]
+    bad[3][5] = tables[3].shape[0] + 12345  # far outside the table
+    bad[4][0] = -1
+    out = mod(to_device(bad), to_device(offsets))
+    with pytest.raises(EbError):
+        mod.check_status()
+    # the rest of the output is still right: rows with a bad index miss only that term
+    good = mod(to_device(values), to_device(offsets))
+    mod.check_status()
+    col3 = sum(t.shape[1] for t in tables[:3])
+    assert torch.equal(out[:, :col3], good[:, :col3])
+    # decreasing offsets are clamped and reported
+    o_bad = [o.copy() for o in offsets]
+    o_bad[2][10] = o_bad[2][9] - 1 if o_bad[2][9] > 0 else 0
+    o_bad[2][7] = 10 ** 6
+    mod(to_device(values), to_device(o_bad))
+    with pytest.raises(EbError):
+        mod.check_status()
+
+
+def test_timing_returns_per_feature_times(cfg1):
+    cfg, tables, values, offsets, mod = cfg1
+    mod.set_schedules(all_schedules("flat", 4, len(tables)))
+    out, times = mod(to_device(values), to_device(offsets), timing=True)
+    check_against_oracle(out, tables, values, offsets, "f32")
+    assert times.shape == (len(tables),) and times.dtype == torch.float64
+    assert torch.all(times > 0)
+    out, times = mod(to_device(values), to_device(offsets), timing=True, timing_schedules=3)
+    assert times.shape == (3,)
+
+
+def test_text_front_end_matches_reference_module_contract():
+    """FeatProcessEmbed.forward(raw_data): strings in, [batch, sum(dim)] out (reference: rec_modules.py:127-140)."""
+    from recflex_b200.rec_modules import FeatProcessEmbed
+
+    rng = np.random.default_rng(11)
+    shapes = [(100, 16), (57, 16), (300, 32)]
+    tables = [(rng.standard_normal(s) * 0.1).astype(np.float32) for s in shapes]
+    batch = 40
+    raw, values, offsets = [], [], []
+    for rows, _ in shapes:
+        lines = []
+        for _b in range(batch):
+            n = int(rng.integers(0, 6))
+            lines.append(",".join(str(int(x)) for x in rng.integers(0, rows, n)))
+        raw.append(lines)
+        v, o = oracle.parse_bags(lines)
+        values.append(v)
+        offsets.append(o)
+    model = FeatProcessEmbed(None, 0, embed_tables=device_tables(tables))
+    out = model(raw)
+    check_against_oracle(out, tables, values, offsets, "f32")
+    (out2, ms) = model(raw, timing_kernel=True)
+    assert torch.equal(out, out2) and ms > 0
+
+
+def test_synthetic_table_fill_is_bit_reproducible_on_cpu():
+    cfg = synth.make_config(3, row_scale=1e-4, batch=8)
+    dev = synth.make_tables_device(cfg, "cuda:0")
+    torch.cuda.synchronize()
+    for fs, t in list(zip(cfg.features, dev))[:12]:
+        host = synth.synth_table(fs.seed, fs.rows, fs.dim, fs.dtype)
+        assert np.array_equal(t.cpu().numpy().view(np.uint16), host.view(np.uint16))
+    cfg = synth.make_config(1, row_scale=0.01)
+    for fs, t in zip(cfg.features, synth.make_tables_device(cfg, "cuda:0")):
+        assert np.array_equal(t.cpu().numpy(), synth.synth_table(fs.seed, fs.rows, fs.dim, fs.dtype))
