@@ -55,17 +55,26 @@ extern "C" {
  *                   Replaces obms::SparseSegmentReduce
  *                   (one_block_multi_sample_kernel.cuh:16-108).
  *   EB_SCHED_FLAT   a warp streams the flattened index list of a run of bags,
+ *                   dealing consecutive entries round-robin to its row slots,
  *                   keeps `unroll` rows per lane in flight regardless of bag
  *                   boundaries and resolves the boundaries with a segmented
  *                   warp reduction.  Replaces rbk::SparseSegmentSum
  *                   (reduce_by_key_kernel.cuh:185-366) without its inter-block
  *                   barrier and without leaving empty bags unwritten.
+ *   EB_SCHED_STREAM the same flattened stream cut into one contiguous piece per
+ *                   row slot; each slot walks its piece serially (no reduction
+ *                   inside a piece), bags cut by a piece boundary are patched
+ *                   once per 32 bags with a segmented shuffle scan.  Load
+ *                   balanced over indices like rbk:: and mbs::
+ *                   (multi_block_per_sample_kernel.cuh:17-112) but with neither
+ *                   atomics nor scans in the inner loop.
  *   EB_SCHED_AUTO   let the library choose from dim, dtype and mean bag length.
  */
 #define EB_SCHED_AUTO 0
 #define EB_SCHED_GROUP 1
 #define EB_SCHED_WARP 2
 #define EB_SCHED_FLAT 3
+#define EB_SCHED_STREAM 4
 
 typedef struct eb_handle eb_handle;
 
@@ -73,7 +82,7 @@ typedef struct eb_handle eb_handle;
  * pair (RecFlex/code_emitter/schedule_base.py:54-87). */
 typedef struct eb_schedule {
   int32_t kind;          /* EB_SCHED_* */
-  int32_t unroll;        /* rows kept in flight per lane: 1, 2, 4 or 8 (0 = auto) */
+  int32_t unroll;        /* rows kept in flight per lane: 1, 2, 4 or 8 (0 = auto); batches with 64-bit indices always run at 4 */
   int32_t vec_bytes;     /* bytes per lane per row load: 16 (0 = auto; rows that are not 16-byte multiples use the element-wise fallback) */
   int32_t bags_per_tile; /* bags bound to one warp per tile; 0 = chosen on the device from the batch's mean bag length */
 } eb_schedule;

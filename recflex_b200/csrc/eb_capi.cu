@@ -87,18 +87,18 @@ struct eb_handle {
 
 namespace {
 
-// AUTO resolution: flat streaming with four rows in flight is the robust
-// default; the tuner replaces it per feature.
+// AUTO resolution: the blocked stream walk with four rows in flight is the
+// robust default; the tuner replaces it per feature.
 eb_schedule resolve(const eb_schedule& in) {
   eb_schedule s = in;
-  if (s.kind == EB_SCHED_AUTO) s.kind = EB_SCHED_FLAT;
+  if (s.kind == EB_SCHED_AUTO) s.kind = EB_SCHED_STREAM;
   if (s.unroll == 0) s.unroll = 4;
   if (s.vec_bytes == 0) s.vec_bytes = 16;
   return s;
 }
 
 int check_schedule(const eb_schedule& s, int f) {
-  if (s.kind < EB_SCHED_AUTO || s.kind > EB_SCHED_FLAT)
+  if (s.kind < EB_SCHED_AUTO || s.kind > EB_SCHED_STREAM)
     return fail(EB_ERR_INVALID_ARG, "feature %d: unknown schedule kind %d", f, s.kind);
   if (!(s.unroll == 0 || s.unroll == 1 || s.unroll == 2 || s.unroll == 4 || s.unroll == 8))
     return fail(EB_ERR_INVALID_ARG, "feature %d: unroll must be 0, 1, 2, 4 or 8 (got %d)", f, s.unroll);

@@ -12,19 +12,53 @@ namespace ebk {
 // ---------------------------------------------------------------------------
 // schedule dispatch
 // ---------------------------------------------------------------------------
-#define EB_DISPATCH_UNROLL(FN, T, V)                          \
-  switch (fs.unroll) {                                        \
-    case 1: FN<T, V, 1>(ctx, b0, b1, lane); break;            \
-    case 2: FN<T, V, 2>(ctx, b0, b1, lane); break;            \
-    case 4: FN<T, V, 4>(ctx, b0, b1, lane); break;            \
-    default: FN<T, V, 8>(ctx, b0, b1, lane); break;           \
+#define EB_DISPATCH_UNROLL(FN, T, V, I64)                          \
+  switch (fs.unroll) {                                             \
+    case 1: FN<T, V, 1, I64>(ctx, b0, b1, lane); break;            \
+    case 2: FN<T, V, 2, I64>(ctx, b0, b1, lane); break;            \
+    case 4: FN<T, V, 4, I64>(ctx, b0, b1, lane); break;            \
+    default: FN<T, V, 8, I64>(ctx, b0, b1, lane); break;           \
   }
 
-#define EB_DISPATCH_DTYPE(FN)                                 \
-  if (fs.dtype == 1) {                                        \
-    EB_DISPATCH_UNROLL(FN, __half, 8)                         \
-  } else {                                                    \
-    EB_DISPATCH_UNROLL(FN, float, 4)                          \
+#define EB_DISPATCH_DTYPE(FN, I64)                                 \
+  if (fs.dtype == 1) {                                             \
+    EB_DISPATCH_UNROLL(FN, __half, 8, I64)                         \
+  } else {                                                         \
+    EB_DISPATCH_UNROLL(FN, float, 4, I64)                          \
+  }
+
+// 64-bit indices are the uncommon case: every schedule kind is instantiated for
+// them, but only at unroll 4 (the requested unroll is ignored).
+#define EB_DISPATCH_DTYPE_U4(FN, I64)                              \
+  if (fs.dtype == 1) FN<__half, 8, 4, I64>(ctx, b0, b1, lane);     \
+  else FN<float, 4, 4, I64>(ctx, b0, b1, lane);
+
+#define EB_DISPATCH_KIND64()                                       \
+  if (!fs.vec) {                                                   \
+    if (fs.dtype == 1) tile_warp<__half, 1, 4, true>(ctx, b0, b1, lane); \
+    else tile_warp<float, 1, 4, true>(ctx, b0, b1, lane);          \
+  } else if (fs.kind == 1) {                                       \
+    EB_DISPATCH_DTYPE_U4(tile_group, true)                         \
+  } else if (fs.kind == 2) {                                       \
+    EB_DISPATCH_DTYPE_U4(tile_warp, true)                          \
+  } else if (fs.kind == 3) {                                       \
+    EB_DISPATCH_DTYPE_U4(tile_flat, true)                          \
+  } else {                                                         \
+    EB_DISPATCH_DTYPE_U4(tile_stream, true)                        \
+  }
+
+#define EB_DISPATCH_KIND(I64)                                      \
+  if (!fs.vec) {                                                   \
+    if (fs.dtype == 1) tile_warp<__half, 1, 4, I64>(ctx, b0, b1, lane); \
+    else tile_warp<float, 1, 4, I64>(ctx, b0, b1, lane);           \
+  } else if (fs.kind == 1) {                                       \
+    EB_DISPATCH_DTYPE(tile_group, I64)                             \
+  } else if (fs.kind == 2) {                                       \
+    EB_DISPATCH_DTYPE(tile_warp, I64)                              \
+  } else if (fs.kind == 3) {                                       \
+    EB_DISPATCH_DTYPE(tile_flat, I64)                              \
+  } else {                                                         \
+    EB_DISPATCH_DTYPE(tile_stream, I64)                            \
   }
 
 template <int OCC, bool TIMING>
@@ -82,15 +116,10 @@ __global__ void __launch_bounds__(kCtaThreads, OCC) eb_fused_kernel(LaunchArgs a
     long long c0 = 0;
     if (TIMING) c0 = clock64();
 
-    if (!fs.vec) {
-      if (fs.dtype == 1) tile_warp<__half, 1, 4>(ctx, b0, b1, lane);
-      else tile_warp<float, 1, 4>(ctx, b0, b1, lane);
-    } else if (fs.kind == 1) {
-      EB_DISPATCH_DTYPE(tile_group)
-    } else if (fs.kind == 2) {
-      EB_DISPATCH_DTYPE(tile_warp)
+    if (a.idx64) {
+      EB_DISPATCH_KIND64()
     } else {
-      EB_DISPATCH_DTYPE(tile_flat)
+      EB_DISPATCH_KIND(false)
     }
 
     if (TIMING) {
@@ -104,5 +133,8 @@ __global__ void __launch_bounds__(kCtaThreads, OCC) eb_fused_kernel(LaunchArgs a
 
 #undef EB_DISPATCH_UNROLL
 #undef EB_DISPATCH_DTYPE
+#undef EB_DISPATCH_KIND
+#undef EB_DISPATCH_KIND64
+#undef EB_DISPATCH_DTYPE_U4
 
 }  // namespace ebk

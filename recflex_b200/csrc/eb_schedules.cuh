@@ -7,7 +7,11 @@
 //
 //   tile_group  (EB_SCHED_GROUP)  slot-per-bag, serial walk, no reduction
 //   tile_warp   (EB_SCHED_WARP)   warp-per-bag, slots split the bag, butterfly reduce
-//   tile_flat   (EB_SCHED_FLAT)   flattened entry stream, segmented reduce at bag boundaries
+//   tile_flat   (EB_SCHED_FLAT)   flattened entry stream dealt round-robin to the slots,
+//                                 segmented reduce at bag boundaries
+//   tile_stream (EB_SCHED_STREAM) flattened entry stream cut into one contiguous piece per
+//                                 slot; each slot walks its piece serially, bags that
+//                                 straddle pieces are patched once per 32 bags
 //
 // They cover the same ground as the reference's ws:: / onehot:: / obms:: / rbk::
 // device templates (examples/csrc/include/*_kernel.cuh) but share one load/store
@@ -71,11 +75,18 @@ struct RowOps<__half, 8> {
   using Raw = uint4;
   __device__ __forceinline__ static Raw zero() { return make_uint4(0, 0, 0, 0); }
   __device__ __forceinline__ static Raw load(const char* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+  // sm_100 mixed-precision add: fp32 accumulator += binary16 operand, one
+  // instruction per element instead of convert + add; same rounding (the
+  // binary16 value is exact in fp32, the sum is rounded to nearest even).
   __device__ __forceinline__ static void add2(float& x, float& y, unsigned w) {
-    const __half2 h = *reinterpret_cast<const __half2*>(&w);
-    const float2 f = __half22float2(h);
-    x += f.x;
-    y += f.y;
+    asm("{\n\t"
+        ".reg .b16 lo, hi;\n\t"
+        "mov.b32 {lo, hi}, %2;\n\t"
+        "add.f32.f16 %0, lo, %0;\n\t"
+        "add.f32.f16 %1, hi, %1;\n\t"
+        "}"
+        : "+f"(x), "+f"(y)
+        : "r"(w));
   }
   __device__ __forceinline__ static void add(float (&a)[8], const Raw& r) {
     add2(a[0], a[1], r.x);
@@ -177,23 +188,39 @@ __device__ __forceinline__ Chunk load_chunk(const TileCtx& c, int64_t bb, int nb
   return ch;
 }
 
-// Fetch U rows for positions p[u] of the chunk-relative entry list.
-template <typename T, int V, int U>
-__device__ __forceinline__ void fetch_rows(const TileCtx& c, const char* vals, const char* tcol,
-                                           const int (&p)[U], const bool (&ok)[U],
+// Index element type of a batch.
+template <bool IDX64>
+struct IdxOf { using type = int; };
+template <>
+struct IdxOf<true> { using type = long long; };
+
+// Fetch U rows: indices vp[p[u]] -> rows.  With 32-bit indices the bounds check
+// is one unsigned compare and the row address one 32x32+64 multiply-add.
+// CHECK = false skips the per-entry `ok` predicate (every entry is in range).
+template <typename T, int V, int U, bool IDX64, bool CHECK>
+__device__ __forceinline__ void fetch_rows(const TileCtx& c, const typename IdxOf<IDX64>::type* vp,
+                                           const char* tcol, bool col_ok, const int (&p)[U], const bool (&ok)[U],
                                            typename RowOps<T, V>::Raw (&rows)[U]) {
   using Ops = RowOps<T, V>;
-  int64_t idx[U];
+  typename IdxOf<IDX64>::type idx[U];
 #pragma unroll
-  for (int u = 0; u < U; ++u) idx[u] = ok[u] ? load_index(vals, p[u], c.idx64) : 0;
+  for (int u = 0; u < U; ++u) idx[u] = (col_ok && (!CHECK || ok[u])) ? __ldg(vp + p[u]) : 0;
+  const unsigned rows32 = c.rows > 0x80000000ll ? 0x80000000u : (unsigned)c.rows;
 #pragma unroll
   for (int u = 0; u < U; ++u) {
     rows[u] = Ops::zero();
-    if (ok[u]) {
-      if ((uint64_t)idx[u] < (uint64_t)c.rows)
-        rows[u] = Ops::load(tcol + idx[u] * (int64_t)c.row_bytes);
-      else
-        flag(c.status, kStatusBadIndex);
+    if (col_ok && (!CHECK || ok[u])) {
+      if constexpr (IDX64) {
+        if ((uint64_t)idx[u] < (uint64_t)c.rows)
+          rows[u] = Ops::load(tcol + idx[u] * (int64_t)c.row_bytes);
+        else
+          flag(c.status, kStatusBadIndex);
+      } else {
+        if ((unsigned)idx[u] < rows32)
+          rows[u] = Ops::load(tcol + (uint64_t)(unsigned)idx[u] * (unsigned)c.row_bytes);
+        else
+          flag(c.status, kStatusBadIndex);
+      }
     }
   }
 }
@@ -201,7 +228,7 @@ __device__ __forceinline__ void fetch_rows(const TileCtx& c, const char* vals, c
 // ---------------------------------------------------------------------------
 // EB_SCHED_GROUP: each slot owns one bag at a time and walks it serially.
 // ---------------------------------------------------------------------------
-template <typename T, int V, int U>
+template <typename T, int V, int U, bool IDX64>
 __device__ __forceinline__ void tile_group(const TileCtx& c, int64_t b0, int64_t b1, int lane) {
   using Ops = RowOps<T, V>;
   const int lgG = c.lg_group, G = 1 << lgG, R = 32 >> lgG;
@@ -214,7 +241,7 @@ __device__ __forceinline__ void tile_group(const TileCtx& c, int64_t b0, int64_t
     for (int64_t bb = b0; bb < b1; bb += 32) {
       const int nb = (int)((b1 - bb) < 32 ? (b1 - bb) : 32);
       const Chunk ch = load_chunk(c, bb, nb, lane);
-      const char* vals = c.values + ch.e0 * (c.idx64 ? 8 : 4);
+      const typename IdxOf<IDX64>::type* vals = reinterpret_cast<const typename IdxOf<IDX64>::type*>(c.values) + ch.e0;
       for (int i0 = 0; i0 < nb; i0 += R) {
         const int bi = i0 + r;
         const int s = __shfl_sync(kFull, ch.lo, bi & 31);
@@ -230,9 +257,9 @@ __device__ __forceinline__ void tile_group(const TileCtx& c, int64_t b0, int64_t
 #pragma unroll
           for (int u = 0; u < U; ++u) {
             p[u] = s + q + u;
-            ok[u] = col_ok && (q + u < len);
+            ok[u] = q + u < len;
           }
-          fetch_rows<T, V, U>(c, vals, tcol, p, ok, rows);
+          fetch_rows<T, V, U, IDX64, true>(c, vals, tcol, col_ok, p, ok, rows);
 #pragma unroll
           for (int u = 0; u < U; ++u) Ops::add(acc, rows[u]);
         }
@@ -245,7 +272,7 @@ __device__ __forceinline__ void tile_group(const TileCtx& c, int64_t b0, int64_t
 // ---------------------------------------------------------------------------
 // EB_SCHED_WARP: the warp owns one bag at a time; its R slots split the bag.
 // ---------------------------------------------------------------------------
-template <typename T, int V, int U>
+template <typename T, int V, int U, bool IDX64>
 __device__ __forceinline__ void tile_warp(const TileCtx& c, int64_t b0, int64_t b1, int lane) {
   using Ops = RowOps<T, V>;
   const int lgG = c.lg_group, G = 1 << lgG, R = 32 >> lgG;
@@ -258,7 +285,7 @@ __device__ __forceinline__ void tile_warp(const TileCtx& c, int64_t b0, int64_t 
     for (int64_t bb = b0; bb < b1; bb += 32) {
       const int nb = (int)((b1 - bb) < 32 ? (b1 - bb) : 32);
       const Chunk ch = load_chunk(c, bb, nb, lane);
-      const char* vals = c.values + ch.e0 * (c.idx64 ? 8 : 4);
+      const typename IdxOf<IDX64>::type* vals = reinterpret_cast<const typename IdxOf<IDX64>::type*>(c.values) + ch.e0;
       for (int i = 0; i < nb; ++i) {
         const int s = __shfl_sync(kFull, ch.lo, i);
         const int e = __shfl_sync(kFull, ch.hi, i);
@@ -271,9 +298,9 @@ __device__ __forceinline__ void tile_warp(const TileCtx& c, int64_t b0, int64_t 
 #pragma unroll
           for (int u = 0; u < U; ++u) {
             p[u] = q + u * R + r;
-            ok[u] = col_ok && p[u] < e;
+            ok[u] = p[u] < e;
           }
-          fetch_rows<T, V, U>(c, vals, tcol, p, ok, rows);
+          fetch_rows<T, V, U, IDX64, true>(c, vals, tcol, col_ok, p, ok, rows);
 #pragma unroll
           for (int u = 0; u < U; ++u) Ops::add(acc, rows[u]);
         }
@@ -299,7 +326,7 @@ __device__ __forceinline__ void tile_warp(const TileCtx& c, int64_t b0, int64_t 
 // segmented shuffle reduction, stores the ones that also end there, and keeps
 // the last one as the new open bag.
 // ---------------------------------------------------------------------------
-template <typename T, int V, int U>
+template <typename T, int V, int U, bool IDX64>
 __device__ __forceinline__ void tile_flat(const TileCtx& c, int64_t b0, int64_t b1, int lane) {
   using Ops = RowOps<T, V>;
   const int lgG = c.lg_group, G = 1 << lgG, R = 32 >> lgG;
@@ -312,7 +339,7 @@ __device__ __forceinline__ void tile_flat(const TileCtx& c, int64_t b0, int64_t 
     for (int64_t bb = b0; bb < b1; bb += 32) {
       const int nb = (int)((b1 - bb) < 32 ? (b1 - bb) : 32);
       const Chunk ch = load_chunk(c, bb, nb, lane);
-      const char* vals = c.values + ch.e0 * (c.idx64 ? 8 : 4);
+      const typename IdxOf<IDX64>::type* vals = reinterpret_cast<const typename IdxOf<IDX64>::type*>(c.values) + ch.e0;
       const int n = ch.n;
       const bool nonempty = ch.hi > ch.lo;
       float* orow = ocol + bb * c.out_ld;
@@ -344,9 +371,9 @@ __device__ __forceinline__ void tile_flat(const TileCtx& c, int64_t b0, int64_t 
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           p[u] = base + u * R + r;
-          ok[u] = col_ok && p[u] < n;
+          ok[u] = p[u] < n;
         }
-        fetch_rows<T, V, U>(c, vals, tcol, p, ok, rows);
+        fetch_rows<T, V, U, IDX64, true>(c, vals, tcol, col_ok, p, ok, rows);
 
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -423,6 +450,157 @@ __device__ __forceinline__ void tile_flat(const TileCtx& c, int64_t b0, int64_t 
               }
             }
           }
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// EB_SCHED_STREAM: the chunk's n entries are cut into R contiguous pieces of
+// ceil(n / R) entries, one per slot.  Every slot walks its piece serially with
+// U rows in flight, whatever the bag lengths: a bag that ends inside the piece
+// is stored at once (a warp vote guards the store path, so steps without a
+// boundary pay one vote).  While a whole macro-step of U entries stays inside
+// the current bag for every slot, the walk is a pure load + accumulate loop.
+// A bag cut by a piece boundary leaves a tail partial in the slot's
+// accumulator and a head partial in the output row; after the walk a segmented
+// shuffle scan over the slots' tails patches each head (once per 32 bags).
+// ---------------------------------------------------------------------------
+template <typename T, int V, int U, bool IDX64>
+__device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_t b1, int lane) {
+  using Ops = RowOps<T, V>;
+  using IdxT = typename IdxOf<IDX64>::type;
+  const int lgG = c.lg_group, lgR = 5 - lgG, G = 1 << lgG, R = 1 << lgR;
+  const int r = lane >> lgG, cl = lane & (G - 1);
+  for (int xc = 0; xc < c.nx; ++xc) {
+    const int cs = (xc * G + cl) * V;
+    const bool col_ok = cs < c.dim;
+    const char* tcol = c.table + (size_t)cs * sizeof(T);
+    float* ocol = c.out + cs;
+    for (int64_t bb = b0; bb < b1; bb += 32) {
+      const int nb = (int)((b1 - bb) < 32 ? (b1 - bb) : 32);
+      const Chunk ch = load_chunk(c, bb, nb, lane);
+      const int n = ch.n;
+      float* orow = ocol + bb * c.out_ld;
+      const unsigned nz = __ballot_sync(kFull, ch.hi > ch.lo);
+
+      // empty bags pool to zero: slot r takes the r-th remaining one
+      {
+        const unsigned valid = nb == 32 ? kFull : ((1u << nb) - 1u);
+        unsigned em = ~nz & valid;
+        float z[V];
+        zero_vals<V>(z);
+        while (em) {
+          const int i = (int)__fns(em, 0, r + 1);
+          if (i >= 0 && col_ok) store_vals<V>(orow + (int64_t)i * c.out_ld, z, c.out_vec);
+          for (int k = 0; k < R && em; ++k) em &= em - 1;
+        }
+      }
+      if (n == 0) continue;
+
+      // my piece [s, e_end) and the bag that holds its first entry
+      const int ls = (n + R - 1) >> lgR;
+      const int s = min(r * ls, n);
+      const int e_end = min(s + ls, n);
+      int kb = 0;
+#pragma unroll
+      for (int step = 16; step >= 1; step >>= 1) {
+        const int t = __shfl_sync(kFull, ch.hi, kb + step - 1);
+        if (t <= s) kb += step;
+      }
+      int kend = __shfl_sync(kFull, ch.hi, kb);
+      bool head_pending = __shfl_sync(kFull, ch.lo, kb) < s;  // my first bag began in an earlier piece
+      bool had_head = false;
+      int head_bag = 0;
+      int e = s;
+      const IdxT* vp = reinterpret_cast<const IdxT*>(c.values) + ch.e0;
+      float acc[V];
+      zero_vals<V>(acc);
+
+      for (int k = 0; k < ls; k += U) {
+        int p[U];
+        bool ok[U];
+        typename Ops::Raw rows[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          p[u] = e + u;
+          ok[u] = p[u] < e_end;
+        }
+        const bool inner = (e + U < kend) && (e + U <= e_end);
+        if (__all_sync(kFull, inner)) {
+          fetch_rows<T, V, U, IDX64, false>(c, vp, tcol, col_ok, p, ok, rows);
+#pragma unroll
+          for (int u = 0; u < U; ++u) Ops::add(acc, rows[u]);
+          e += U;
+        } else {
+          fetch_rows<T, V, U, IDX64, true>(c, vp, tcol, col_ok, p, ok, rows);
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            Ops::add(acc, rows[u]);
+            const bool at_end = ok[u] && (e + 1 == kend);
+            if (__any_sync(kFull, at_end)) {
+              const unsigned rest = kb >= 31 ? 0u : (nz & (0xfffffffeu << kb));
+              const int nkb = rest ? (__ffs(rest) - 1) : 31;
+              int nend = __shfl_sync(kFull, ch.hi, nkb);
+              if (!rest) nend = 0x7fffffff;
+              if (at_end) {
+                if (col_ok) store_vals<V>(orow + (int64_t)kb * c.out_ld, acc, c.out_vec);
+                if (head_pending) {
+                  had_head = true;
+                  head_bag = kb;
+                  head_pending = false;
+                }
+                zero_vals<V>(acc);
+                kb = nkb;
+                kend = nend;
+              }
+            }
+            e += ok[u] ? 1 : 0;
+          }
+        }
+      }
+
+      // patch the bags cut by piece boundaries
+      if (R > 1 && __any_sync(kFull, had_head)) {
+        bool f = !(head_pending && e_end > s);  // my tail starts a new run unless my whole piece lies inside one bag
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          if (d < R) {
+            const bool take = (r >= d) && !f;
+            const int fv = __shfl_up_sync(kFull, (int)f, d << lgG);
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+              const float y = __shfl_up_sync(kFull, acc[k], d << lgG);
+              if (take) acc[k] += y;
+            }
+            if (take) f = fv != 0;
+          }
+        }
+        float prev[V];
+#pragma unroll
+        for (int k = 0; k < V; ++k) prev[k] = __shfl_up_sync(kFull, acc[k], G);
+        if (had_head && col_ok) {
+          float* dst = orow + (int64_t)head_bag * c.out_ld;
+          float hv[V];
+          if constexpr (V == 1) {
+            hv[0] = dst[0] + prev[0];
+          } else {
+            if (c.out_vec) {
+#pragma unroll
+              for (int k = 0; k < V; k += 4) {
+                const float4 q = *reinterpret_cast<const float4*>(dst + k);
+                hv[k] = q.x + prev[k];
+                hv[k + 1] = q.y + prev[k + 1];
+                hv[k + 2] = q.z + prev[k + 2];
+                hv[k + 3] = q.w + prev[k + 3];
+              }
+            } else {
+#pragma unroll
+              for (int k = 0; k < V; ++k) hv[k] = dst[k] + prev[k];
+            }
+          }
+          store_vals<V>(dst, hv, c.out_vec);
         }
       }
     }
