@@ -227,6 +227,39 @@ int eb_fill_table(void* table, int64_t rows, int32_t dim, int32_t table_dtype, u
 int eb_parse_bags(const char* text, size_t text_len, int64_t batch, int32_t* values_out,
                   int64_t values_cap, int32_t* offsets_out, int64_t* nnz_out);
 
+/*
+ * The packed fused forward for callers that cannot allocate device memory at
+ * all: a plugin inside a server whose memory pool owns every byte and treats a
+ * driver allocation as an error, a sandbox that forbids allocation calls, or a
+ * latency path where an allocation's implicit device synchronisation is not
+ * acceptable.  Those callers can use neither eb_create() (it allocates the
+ * descriptor table) nor a workspace of their own.  This entry point has no
+ * counterpart in the reference, whose launcher allocates per call
+ * (RecFlex/code_emitter/codegen.py:416-421).
+ *
+ * It takes the tables directly (same meaning as eb_create's arguments), one
+ * packed batch (as eb_forward_packed) and the output, and calls no cudaMalloc,
+ * cudaFree or other allocating routine.  Descriptors and scratch live in one
+ * array built into the library image (about 121 KB of device memory on every
+ * GPU that loads the library, until the process exits), which bounds it to
+ * EB_NOALLOC_MAX_FEATURES features: more are refused with EB_ERR_TOO_LARGE.
+ * Schedules are the library defaults at 4 CTAs per SM.
+ *
+ * All calls on a GPU share that array and it keeps the previous call's
+ * contents; each call rewrites the descriptors and its binding kernel resets
+ * the counters and the status word, so back-to-back calls on one stream are
+ * safe, while calls that overlap on the GPU (other streams, other host
+ * threads) race.  The host-side staging of the descriptors is a single static
+ * buffer too: do not call this from two host threads at once.  The first call
+ * on each device resolves the array's device address (cudaGetSymbolAddress);
+ * make that first call before any stream capture begins.
+ */
+#define EB_NOALLOC_MAX_FEATURES 1024
+int eb_forward_packed_noalloc(int device, int num_features, const int64_t* rows, const int32_t* dims,
+                              const int32_t* table_dtype, const void* const* table_ptrs, int64_t batch,
+                              const void* values, const void* offsets, int index_dtype, float* out,
+                              int64_t out_ld, void* stream);
+
 /* Message of the calling thread's last failure ("" if none). */
 const char* eb_last_error(void);
 

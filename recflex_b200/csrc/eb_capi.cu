@@ -65,6 +65,10 @@ int ilog2(int x) {
 
 }  // namespace
 
+namespace ebk {
+void set_last_error(const char* msg) { g_err = msg ? msg : ""; }
+}  // namespace ebk
+
 struct eb_handle {
   int device = 0;
   int num_features = 0;
