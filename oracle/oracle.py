@@ -81,13 +81,11 @@ def pool_numpy(tables: Sequence[np.ndarray], values: Sequence[np.ndarray], offse
     for t, v, o in zip(tables, values, offsets):
         res = np.zeros((batch, t.shape[1]), dtype=np.float64)
         gathered = t[np.asarray(v, dtype=np.int64)].astype(np.float64)
-        csum = np.concatenate([np.zeros((1, t.shape[1])), np.cumsum(gathered, axis=0)])
         o = np.asarray(o, dtype=np.int64)
-        # exact per-bag sums for short bags; cumulative differences would lose bits, so loop the bags
+        # loop the bags: differences of a running sum would lose bits
         for b in range(batch):
             if o[b + 1] > o[b]:
                 res[b] = gathered[o[b]:o[b + 1]].sum(axis=0)
-        del csum
         cols.append(res)
     return np.concatenate(cols, axis=1).astype(np.float32)
 
