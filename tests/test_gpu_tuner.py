@@ -1,0 +1,66 @@
+"""GPU: the two-stage tuner picks schedules, keeps parity, round-trips through JSON."""
+import os
+
+import pytest
+import torch
+
+from recflex_b200.rec_modules import FeatEmbed, Schedule
+from recflex_b200.tuning import TuneConfig, Tuner, TuneResult
+from tests.helpers import check_against_oracle, device_tables, small_model, to_device
+
+pytestmark = pytest.mark.gpu
+
+
+def test_tuner_end_to_end(tmp_path):
+    cfg, tables, values, offsets = small_model(2, 0.02, 2048)
+    mod = FeatEmbed("cuda:0", embed_tables=device_tables(tables))
+    dv, do = to_device(values), to_device(offsets)
+    tc = TuneConfig(occupancies=(4, 8), reps=1, global_reps=2, min_replicas=16)
+    tuner = Tuner(mod, [(dv, do)], tc)
+    assert len(tuner.clusters()) < len(tables)  # look-alike features share one representative
+    res = tuner.tune()
+    assert res.occupancy in (4, 8) and len(res.schedules) == len(tables)
+    assert set(res.global_ms) == {4, 8} and all(v > 0 for v in res.global_ms.values())
+    # local stage measured every candidate of every feature at every occupancy
+    for f in range(len(tables)):
+        for occ in (4, 8):
+            assert len(res.local_times[f][occ]) == len(tuner._cands[f])
+            assert all(t > 0 for t in res.local_times[f][occ])
+    # the tuned module still computes the right thing
+    got, occ = mod.get_schedules()
+    assert occ == res.occupancy and got == res.schedules
+    out = mod(dv, do)
+    mod.check_status()
+    check_against_oracle(out, tables, values, offsets, "f32")
+    # persistence
+    path = os.path.join(tmp_path, "tuned.json")
+    res.save(path, workload=cfg.name)
+    back = TuneResult.load(path)
+    assert back.schedules == res.schedules and back.occupancy == res.occupancy
+    # one-hot features never get a multi-row unroll from warp/group candidates
+    onehot = [f for f, fs in enumerate(cfg.features) if fs.length == "onehot"]
+    for f in onehot:
+        assert all(not (c.kind in (1, 2) and c.unroll > 1) for c in tuner.candidates(f))
+    # mutation validation: every mutation is timed, the pick is one of them
+    times, pick = tuner.mutation_validation(res, onehot[0])
+    assert len(times) == len(tuner.candidates(onehot[0])) and all(t > 0 for t in times)
+
+
+def test_naive_tuning_and_retune():
+    cfg, tables, values, offsets = small_model(2, 0.02, 512)
+    mod = FeatEmbed("cuda:0", embed_tables=device_tables(tables[:6]))
+    dv, do = to_device(values[:6]), to_device(offsets[:6])
+    tc = TuneConfig(occupancies=(4,), reps=1, global_reps=1, kinds=("warp", "stream"), unrolls=(2, 4))
+    tuner = Tuner(mod, [(dv, do)], tc)
+    res = tuner.tune_naive(occupancy=4)
+    assert len(res.schedules) == 6
+    res = tuner.tune()
+    # shifted inputs: feature 0's bags become 8x longer -> only that feature is re-tuned
+    v0 = torch.cat([dv[0]] * 8)
+    o0 = do[0] * 8
+    shifted = ([v0] + dv[1:], [o0] + do[1:])
+    res2 = tuner.retune(res, [shifted])
+    assert list(res2.local_times) == [0]
+    out = mod(*shifted)
+    mod.check_status()
+    assert torch.isfinite(out).all()

@@ -57,3 +57,11 @@ def test_batches_are_seeded_and_bytes_formula():
     assert synth.algorithmic_bytes(cfg, a[1], 4) == expect
     pv, po = synth.pack_batch(*a)
     assert po.shape == (50, 65) and len(pv) == sum(len(x) for x in a[0])
+
+
+def test_retune_trigger_is_bucketed():
+    from recflex_b200.tuning import InputStats, needs_retune
+
+    old = [InputStats(10.0, 40, 0.0), InputStats(1.0, 1, 0.0), InputStats(3.0, 9, 0.1)]
+    new = [InputStats(11.0, 44, 0.0), InputStats(10.0, 30, 0.0), InputStats(3.1, 9, 0.2)]
+    assert needs_retune(old, new) == [1]
