@@ -328,6 +328,14 @@ def run_ours(args):
                 peak, peak_src = float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
         else:
             peak, peak_src = 6650.0, "fallback"
+        traffic = None  # dram__bytes_read + dram__bytes_write of one full-size launch, from the committed ncu summary
+        prof = os.path.join(ROOT, "profiles", f"eb_fused_kernel_{args.workload}_full_size.md")
+        if os.path.exists(prof) and args.row_scale == 1.0 and not args.batch:
+            import re
+
+            with open(prof) as f:
+                m = re.search(r"dram_bytes_per_launch:\s*(\d+)", f.read())
+            traffic = int(m.group(1)) if m else None
         k_ms = statistics.mean(ktimes) if ktimes else None
         mean_bytes = statistics.mean(alg_bytes[i % nb] for i in range(min(K, 256)))
         achieved = mean_bytes / (k_ms * 1e-3) / 1e9 if k_ms else None
@@ -341,7 +349,7 @@ def run_ours(args):
                        "index_dtype": "int32"},
             "roofline": {
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak if achieved else None, "traffic": None,
+                "frac": achieved / peak if achieved else None, "traffic": traffic,
                 "kernel": "eb_fused_kernel", "kernel_ms": k_ms, "algorithmic_bytes_per_launch": mean_bytes,
                 "peak_source": peak_src,
             },
