@@ -217,6 +217,19 @@ int eb_fill_table(void* table, int64_t rows, int32_t dim, int32_t table_dtype, u
                   float std, int device, void* stream);
 
 /*
+ * Column placement for table-wise sharding (no counterpart in the reference,
+ * which has no multi-GPU data path): after the all-to-all of pooled outputs a
+ * rank holds, back to back, one block [rows, sum(dim of sender s's features)]
+ * per sender.  This copies every feature's columns to its canonical place in
+ * dst [rows, dst_ld].  `segments` is a DEVICE array of num_segments records
+ * {int64 src_off; int32 src_ld; int32 dst_col; int32 width; int32 pad}: element
+ * offset (from src) of the feature's first column in row 0 of its block, the
+ * block's row length, the destination column and the feature's dim.
+ */
+int eb_place_columns(const float* src, float* dst, int64_t rows, int64_t dst_ld, int32_t num_segments,
+                     const void* segments, int device, void* stream);
+
+/*
  * Host-side parser of the reference's text input: `text` holds `batch` lines
  * separated by '\n' (one bag per line, indices separated by any non-digit
  * character, an empty line is an empty bag).  Writes the indices to values_out

@@ -5,6 +5,7 @@
 // per-schedule num_tiles / num_blocks arithmetic of the host preprocess
 // (examples/csrc/*_preprocess.cu).
 // eb_fill_kernel: counter-based synthetic table weights.
+// eb_place_kernel: receive-side column placement of the sharded path.
 // Included by exactly one translation unit (eb_launch.cu).
 #pragma once
 #include "eb_common.cuh"
@@ -175,6 +176,45 @@ __global__ void __launch_bounds__(256) eb_fill_kernel(T* table, int64_t elems, u
     const float w = synth_weight(seed, (uint64_t)i, scale);
     if constexpr (sizeof(T) == 2) table[i] = __float2half_rn(w);
     else table[i] = w;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// column placement: after the all-to-all of pooled outputs, rank-major blocks
+// [rows, sum(dim of the sender's features)] are scattered to each feature's
+// canonical columns of the [rows, dst_ld] result.  One descriptor per feature:
+// {element offset of the feature's first column in row 0 of its block, the
+// block's row length, destination column, width}.
+// ---------------------------------------------------------------------------
+struct PlaceSeg {
+  long long src_off;
+  int src_ld, dst_col, width, pad_;
+};
+
+__global__ void __launch_bounds__(256) eb_place_kernel(const float* __restrict__ src, float* __restrict__ dst,
+                                                       long long rows, long long dst_ld,
+                                                       const PlaceSeg* __restrict__ segs, int vec_ok) {
+  const PlaceSeg sg = segs[blockIdx.y];
+  const float* s0 = src + sg.src_off;
+  float* d0 = dst + sg.dst_col;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const bool v4 = vec_ok && (sg.width & 3) == 0 && (sg.src_ld & 3) == 0 && (sg.src_off & 3) == 0 && (sg.dst_col & 3) == 0;
+  if (v4) {
+    const int w4 = sg.width >> 2;
+    const long long items = rows * w4;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < items; i += stride) {
+      const long long row = i / w4;
+      const int c = (int)(i - row * w4) << 2;
+      const float4 v = __ldcs(reinterpret_cast<const float4*>(s0 + row * sg.src_ld + c));
+      __stcs(reinterpret_cast<float4*>(d0 + row * dst_ld + c), v);
+    }
+  } else {
+    const long long items = rows * sg.width;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < items; i += stride) {
+      const long long row = i / sg.width;
+      const int c = (int)(i - row * sg.width);
+      d0[row * dst_ld + c] = s0[row * sg.src_ld + c];
+    }
   }
 }
 

@@ -495,6 +495,18 @@ int eb_fill_table(void* table, int64_t rows, int32_t dim, int32_t table_dtype, u
   return EB_OK;
 }
 
+int eb_place_columns(const float* src, float* dst, int64_t rows, int64_t dst_ld, int32_t num_segments,
+                     const void* segments, int device, void* stream) {
+  if (rows < 0 || num_segments < 0) return fail(EB_ERR_INVALID_ARG, "negative size");
+  if (rows == 0 || num_segments == 0) return EB_OK;
+  if (!src || !dst || !segments) return fail(EB_ERR_INVALID_ARG, "null pointer");
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(EB_ERR_CUDA, "cannot select device %d", device);
+  const int vec_ok = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0 && dst_ld % 4 == 0;
+  EB_CUDA(launch_place(src, dst, rows, dst_ld, num_segments, segments, vec_ok, static_cast<cudaStream_t>(stream)));
+  return EB_OK;
+}
+
 int eb_parse_bags(const char* text, size_t text_len, int64_t batch, int32_t* values_out, int64_t values_cap,
                   int32_t* offsets_out, int64_t* nnz_out) {
   if ((!text && text_len) || batch < 0 || !offsets_out || !nnz_out || (values_cap > 0 && !values_out))

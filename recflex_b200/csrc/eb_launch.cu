@@ -46,4 +46,18 @@ cudaError_t launch_fill(void* table, int64_t elems, int dtype, uint64_t seed, fl
   return cudaGetLastError();
 }
 
+cudaError_t launch_place(const float* src, float* dst, int64_t rows, int64_t dst_ld, int num_segments,
+                         const void* segments, int vec_ok, cudaStream_t st) {
+  if (rows == 0 || num_segments == 0) return cudaSuccess;
+  int64_t bx = (rows * 8 + 255) / 256;  // a few float4 per thread for the narrowest features
+  if (bx > 148 * 4) bx = 148 * 4;
+  if (bx < 1) bx = 1;
+  for (int first = 0; first < num_segments; first += 65535) {
+    const int n = num_segments - first < 65535 ? num_segments - first : 65535;
+    eb_place_kernel<<<dim3((unsigned)bx, (unsigned)n), 256, 0, st>>>(
+        src, dst, rows, dst_ld, static_cast<const PlaceSeg*>(segments) + first, vec_ok);
+  }
+  return cudaGetLastError();
+}
+
 }  // namespace ebk

@@ -22,6 +22,9 @@ FusedKernel fused_kernel_occ8(bool timing);
 cudaError_t launch_bind(const LaunchArgs& a, bool zero_feature_times, cudaStream_t st);
 cudaError_t launch_fused(const LaunchArgs& a, int occupancy, bool timing, int grid, cudaStream_t st);
 cudaError_t fused_ctas_per_sm(int occupancy, int* per_sm);
+cudaError_t launch_place(const float* src, float* dst, int64_t rows, int64_t dst_ld, int num_segments,
+                         const void* segments, int vec_ok, cudaStream_t st);
+
 // Sets the calling thread's eb_last_error() message (defined beside it).
 void set_last_error(const char* msg);
 

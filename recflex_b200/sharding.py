@@ -1,0 +1,262 @@
+"""Multi-GPU partitioning of the fused embedding-bag forward (one process per GPU, torch.distributed).
+
+The reference has no multi-GPU data path (it uses several GPUs only as independent tuning workers,
+RecFlex/tuning/measure.py:27,68); both modes here are new:
+
+* replicated tables, batch split: every rank holds all tables and pools its own share of the samples
+  with the plain `FeatEmbed`; nothing is exchanged.  Nothing to add beyond `FeatEmbed`.
+* table-wise sharding (`plan_shards` + `ShardedFeatEmbed`): whole tables are assigned to ranks by a
+  size/traffic-balanced planner; each rank pools ITS features for the WHOLE batch, the pooled rows are
+  exchanged with one all-to-all per batch chunk over NCCL (NVLink/NVSwitch), and a placement kernel puts
+  every feature's columns at its canonical position, so that rank r ends with `[B / world, sum(dim)]` for
+  its share of the samples, identical to what the unsharded module computes for those samples.
+
+Batch chunks pipeline the exchange behind the pooling: chunk k's all-to-all runs on a side stream
+while chunk k + 1 is pooled.  With C chunks, sample b of the batch belongs to chunk `b // (B / C)` and,
+inside the chunk, to rank `(b % (B / C)) // (B / (C * world))`; a rank's output rows are its samples in
+batch order.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+
+# ---------------------------------------------------------------------------
+# planner
+# ---------------------------------------------------------------------------
+def plan_shards(table_bytes: Sequence[int], traffic: Sequence[float], world: int,
+                capacity_bytes: Optional[int] = None) -> List[int]:
+    """Owner rank of every table.
+
+    Longest-processing-time greedy on `traffic` (expected gathered bytes per batch: nnz_f * row_bytes_f)
+    under a per-rank capacity on `table_bytes`, then pairwise moves/swaps while they lower the maximum
+    per-rank traffic.  Raises if the tables do not fit.
+    """
+    F = len(table_bytes)
+    if len(traffic) != F or world < 1:
+        raise ValueError("table_bytes and traffic must have one entry per table, world >= 1")
+    cap = capacity_bytes if capacity_bytes is not None else float("inf")
+    if any(b > cap for b in table_bytes):
+        raise ValueError("a single table exceeds the per-rank capacity")
+    owner = [-1] * F
+    load = [0.0] * world
+    used = [0] * world
+    # heaviest traffic first; among equals the bigger table first (harder to place)
+    for f in sorted(range(F), key=lambda i: (-traffic[i], -table_bytes[i])):
+        ranks = [r for r in range(world) if used[r] + table_bytes[f] <= cap]
+        if not ranks:
+            # make room: capacity-aware fallback = rank with the most free bytes must fit it
+            raise ValueError("tables do not fit the per-rank capacity with this greedy order; raise capacity or world")
+        r = min(ranks, key=lambda k: (load[k], used[k]))
+        owner[f], load[r], used[r] = r, load[r] + traffic[f], used[r] + table_bytes[f]
+    # refinement: move or swap between the most and the least loaded rank while the maximum drops
+    for _ in range(4 * F):
+        hi = max(range(world), key=load.__getitem__)
+        lo = min(range(world), key=load.__getitem__)
+        gap = load[hi] - load[lo]
+        if gap <= 0:
+            break
+        best, best_gain = None, 0.0
+        for f in (i for i in range(F) if owner[i] == hi):
+            d = traffic[f]
+            if 0 < d < gap and used[lo] + table_bytes[f] <= cap and min(d, gap - d) > best_gain:
+                best, best_gain = (f, None), min(d, gap - d)
+            for g in (i for i in range(F) if owner[i] == lo):
+                d2 = traffic[f] - traffic[g]
+                if 0 < d2 < gap and used[lo] - table_bytes[g] + table_bytes[f] <= cap \
+                        and used[hi] - table_bytes[f] + table_bytes[g] <= cap and min(d2, gap - d2) > best_gain:
+                    best, best_gain = (f, g), min(d2, gap - d2)
+        if best is None:
+            break
+        f, g = best
+        owner[f] = lo
+        load[hi] -= traffic[f]
+        load[lo] += traffic[f]
+        used[hi] -= table_bytes[f]
+        used[lo] += table_bytes[f]
+        if g is not None:
+            owner[g] = hi
+            load[lo] -= traffic[g]
+            load[hi] += traffic[g]
+            used[lo] -= table_bytes[g]
+            used[hi] += table_bytes[g]
+    return owner
+
+
+def shard_summary(owner: Sequence[int], table_bytes: Sequence[int], traffic: Sequence[float], world: int) -> dict:
+    load = [0.0] * world
+    used = [0] * world
+    for f, r in enumerate(owner):
+        load[r] += traffic[f]
+        used[r] += table_bytes[f]
+    mean = sum(load) / world if world else 0.0
+    return {"bytes_per_rank": used, "traffic_per_rank": load,
+            "traffic_imbalance": (max(load) / mean) if mean > 0 else 1.0}
+
+
+# ---------------------------------------------------------------------------
+# sharded module
+# ---------------------------------------------------------------------------
+class ShardedFeatEmbed:
+    """Table-wise sharded fused forward.
+
+    owner[f]   rank that holds table f (from `plan_shards`); dims[f] = embedding dim of table f.
+    local_tables  this rank's tables in increasing feature order (CUDA tensors), or None together with
+               `pool_fn` for host-side tests.
+    pool_fn    test hook only: `pool_fn(values, offsets, out)` must write the local features' pooled rows
+               `[rows, sum(local dims)]` into `out`; the product path leaves it None and runs the CUDA
+               library through `FeatEmbed`.  place_fn likewise (`place_fn(recv, out, rows)`).
+    """
+
+    def __init__(self, rank: int, world: int, owner: Sequence[int], dims: Sequence[int],
+                 local_tables: Optional[List[torch.Tensor]] = None, device=None, group=None, chunks: int = 4,
+                 pool_fn: Optional[Callable] = None, place_fn: Optional[Callable] = None):
+        if len(owner) != len(dims):
+            raise ValueError("owner and dims must have one entry per feature")
+        self.rank, self.world, self.group = rank, world, group
+        self.owner, self.dims = list(owner), [int(d) for d in dims]
+        self.chunks = max(1, int(chunks))
+        self.local_features = [f for f, r in enumerate(self.owner) if r == rank]
+        self.units = sum(self.dims)
+        self.units_of = [sum(self.dims[f] for f, o in enumerate(self.owner) if o == r) for r in range(world)]
+        self.local_units = self.units_of[rank]
+        col, self.col_of = 0, []
+        for d in self.dims:
+            self.col_of.append(col)
+            col += d
+        self._pool_fn, self._place_fn = pool_fn, place_fn
+        self.local = None
+        if pool_fn is None:
+            if local_tables is None or device is None:
+                raise ValueError("the product path needs this rank's tables on a CUDA device (there is no CPU fallback)")
+            from .rec_modules import FeatEmbed
+
+            if len(local_tables) != len(self.local_features):
+                raise ValueError(f"rank {rank} owns {len(self.local_features)} tables, got {len(local_tables)}")
+            for t, f in zip(local_tables, self.local_features):
+                if int(t.shape[1]) != self.dims[f]:
+                    raise ValueError(f"table of feature {f} has dim {t.shape[1]}, expected {self.dims[f]}")
+            self.device = torch.device(device)
+            self.local = FeatEmbed(self.device, embed_tables=local_tables) if local_tables else None
+            self._lib = _lib.load()
+            self._comm = torch.cuda.Stream(device=self.device)
+        else:
+            self.device = torch.device(device) if device is not None else torch.device("cpu")
+        self._segs = {}      # rows per chunk -> device descriptor tensor for the placement kernel
+        self._bufs = {}
+
+    # -- layout ------------------------------------------------------------
+    def segments(self, rows: int) -> List[Tuple[int, int, int, int]]:
+        """(src_off, src_ld, dst_col, width) of every feature inside a received chunk of `rows` samples:
+        the chunk holds one block [rows, units_of[s]] per sender s, senders in rank order."""
+        segs = []
+        block = 0
+        for s in range(self.world):
+            c = 0
+            for f, o in enumerate(self.owner):
+                if o == s:
+                    segs.append((block + c, self.units_of[s], self.col_of[f], self.dims[f]))
+                    c += self.dims[f]
+            block += rows * self.units_of[s]
+        return segs
+
+    def _segment_tensor(self, rows: int) -> torch.Tensor:
+        t = self._segs.get(rows)
+        if t is None:
+            import numpy as np
+
+            rec = np.zeros(len(self.dims), dtype=[("src_off", "<i8"), ("src_ld", "<i4"), ("dst_col", "<i4"),
+                                                  ("width", "<i4"), ("pad", "<i4")])
+            for i, (so, sl, dc, w) in enumerate(self.segments(rows)):
+                rec[i] = (so, sl, dc, w, 0)
+            t = torch.from_numpy(rec.view(np.uint8).copy()).to(self.device)
+            self._segs[rows] = t
+        return t
+
+    # -- forward -----------------------------------------------------------
+    def forward(self, values: Sequence[torch.Tensor], offsets: Sequence[torch.Tensor],
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """values/offsets: this rank's features (increasing feature order) for the WHOLE batch, offsets with
+        batch + 1 entries.  Returns `[batch / world, sum(dim)]` fp32: this rank's samples, all features."""
+        W, Cn = self.world, self.chunks
+        if len(values) != len(self.local_features) or len(offsets) != len(self.local_features):
+            raise ValueError(f"rank {self.rank} expects {len(self.local_features)} local features")
+        if offsets:
+            batch = offsets[0].numel() - 1
+        else:
+            batch = self._empty_rank_batch
+        if batch % (W * Cn) != 0:
+            raise ValueError(f"batch {batch} must be a multiple of world * chunks = {W * Cn}")
+        bc = batch // Cn          # samples per chunk
+        rows = bc // W            # samples per chunk and rank
+        key = (batch, str(self.device))
+        bufs = self._bufs.get(key)
+        if bufs is None:
+            send = [torch.empty((bc, max(self.local_units, 1)), dtype=torch.float32, device=self.device)
+                    for _ in range(min(Cn, 2))]
+            recv = [torch.empty(rows * self.units, dtype=torch.float32, device=self.device) for _ in range(min(Cn, 2))]
+            bufs = self._bufs[key] = (send, recv)
+        send, recv = bufs
+        if out is None:
+            out = torch.empty((batch // W, self.units), dtype=torch.float32, device=self.device)
+        in_split = [rows * self.local_units] * W
+        out_split = [rows * self.units_of[s] for s in range(W)]
+        cuda = self._pool_fn is None
+        events = []
+        for k in range(Cn):
+            sb, rb = send[k % len(send)], recv[k % len(recv)]
+            if cuda and k >= len(send):
+                torch.cuda.current_stream(self.device).wait_event(events[k - len(send)])  # buffer reuse
+            offs_k = [o[k * bc: (k + 1) * bc + 1] for o in offsets]
+            if self.local_units:
+                if cuda:
+                    self.local(values, offs_k, out=sb)
+                else:
+                    self._pool_fn(values, offs_k, sb)
+            out_k = out[k * rows: (k + 1) * rows]
+            if cuda:
+                ready = torch.cuda.Event()
+                ready.record()
+                with torch.cuda.stream(self._comm):
+                    self._comm.wait_event(ready)
+                    dist.all_to_all_single(rb, sb.view(-1)[: bc * self.local_units], out_split, in_split,
+                                           group=self.group)
+                    self._place(rb, out_k, rows)
+                    done = torch.cuda.Event()
+                    done.record()
+                events.append(done)
+            else:
+                dist.all_to_all_single(rb, sb.reshape(-1)[: bc * self.local_units].contiguous(), out_split, in_split,
+                                       group=self.group)
+                self._place_fn(rb, out_k, rows)
+        if cuda:
+            torch.cuda.current_stream(self.device).wait_stream(self._comm)
+        return out
+
+    __call__ = forward
+
+    _empty_rank_batch = 0
+
+    def set_batch_for_empty_rank(self, batch: int) -> None:
+        """A rank that owns no table cannot read the batch size from its inputs; tell it."""
+        self._empty_rank_batch = int(batch)
+
+    def _place(self, recv: torch.Tensor, out_k: torch.Tensor, rows: int) -> None:
+        segs = self._segment_tensor(rows)
+        _lib.check(self._lib.eb_place_columns(C.c_void_p(recv.data_ptr()), C.c_void_p(out_k.data_ptr()), rows,
+                                              out_k.stride(0), len(self.dims), C.c_void_p(segs.data_ptr()),
+                                              self.device.index,
+                                              C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)))
+
+
+def local_sample_ids(batch: int, world: int, chunks: int, rank: int) -> List[int]:
+    """Batch positions of the samples rank `rank` ends up with, in its output row order."""
+    bc = batch // chunks
+    rows = bc // world
+    return [k * bc + rank * rows + j for k in range(chunks) for j in range(rows)]

@@ -252,6 +252,29 @@ def pack_batch(values: Sequence[np.ndarray], offsets: Sequence[np.ndarray]) -> T
     return np.concatenate(values), np.stack(offsets)
 
 
+def expected_traffic(cfg: ModelConfig, batch: Optional[int] = None) -> List[float]:
+    """Expected gathered bytes per batch of every feature (mean bag length x batch x row bytes): the
+    planner's traffic estimate."""
+    B = batch or cfg.batch
+    out = []
+    for fs in cfg.features:
+        if fs.length == "onehot":
+            mean = 1.0
+        elif fs.length == "empty":
+            mean = 0.0
+        elif fs.length == "uniform":
+            mean = (fs.length_args[0] + fs.length_args[1]) / 2.0
+        elif fs.length == "poisson":
+            mean = fs.length_args[0]
+        else:
+            expo, max_len, empty_frac = fs.length_args
+            l = np.arange(1, max_len + 1, dtype=np.float64)
+            pmf = l ** (-expo)
+            mean = float((l * pmf).sum() / pmf.sum()) * (1.0 - empty_frac)
+        out.append(mean * B * fs.row_bytes)
+    return out
+
+
 def algorithmic_bytes(cfg: ModelConfig, offsets: Sequence[np.ndarray], index_bytes: int = 4) -> int:
     """Roofline numerator of one batch: gathered row bytes + index bytes + offset bytes."""
     total = 0
@@ -266,8 +289,8 @@ def make_tables_numpy(cfg: ModelConfig) -> List[np.ndarray]:
     return [synth_table(fs.seed, fs.rows, fs.dim, fs.dtype) for fs in cfg.features]
 
 
-def make_tables_device(cfg: ModelConfig, device) -> list:
-    """All tables on `device`, filled by the library's counter-based generator."""
+def make_tables_device(cfg: ModelConfig, device, features: Optional[Sequence[int]] = None) -> list:
+    """Tables on `device` (all of them, or only `features`), filled by the library's counter-based generator."""
     import ctypes as C
 
     import torch
@@ -279,7 +302,7 @@ def make_tables_device(cfg: ModelConfig, device) -> list:
     idx = dev.index if dev.index is not None else torch.cuda.current_device()
     stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
     tables = []
-    for fs in cfg.features:
+    for fs in (cfg.features if features is None else [cfg.features[f] for f in features]):
         t = torch.empty((fs.rows, fs.dim), dtype=torch.float16 if fs.dtype == "f16" else torch.float32, device=dev)
         _lib.check(lib.eb_fill_table(C.c_void_p(t.data_ptr()), fs.rows, fs.dim,
                                      _lib.EB_F16 if fs.dtype == "f16" else _lib.EB_F32, fs.seed, WEIGHT_STD, idx,

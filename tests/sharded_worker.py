@@ -1,0 +1,96 @@
+"""Worker of the sharded-path tests: one process per rank (gloo on CPU with test hooks, or nccl on GPUs).
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node W --master-addr 127.0.0.1 --master-port P \
+        tests/sharded_worker.py --backend gloo|nccl [--chunks C]
+
+Every rank builds the same small model and batch from a seed, shards the tables with the planner, runs the
+sharded forward and compares its rows with the oracle's result for the whole batch.  With gloo the pooling
+and placement hooks are the CPU oracle / torch (test infrastructure); with nccl the product path runs.
+"""
+import argparse
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from oracle import oracle
+from recflex_b200.sharding import ShardedFeatEmbed, local_sample_ids, plan_shards, shard_summary
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--backend", default="gloo")
+    ap.add_argument("--chunks", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=48)
+    args = ap.parse_args()
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    if args.backend == "nccl":
+        torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+        dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+        dist.init_process_group("nccl", device_id=dev)
+    else:
+        dev = torch.device("cpu")
+        dist.init_process_group("gloo")
+
+    rng = np.random.default_rng(123)
+    dims = [16, 4, 64, 8, 32, 128, 16, 256, 8]
+    rows = [50, 1000, 70, 33, 400, 90, 64, 20, 5000]
+    dtypes = [np.float32, np.float16]
+    tables = [(rng.standard_normal((r, d)) * 0.1).astype(dtypes[i % 2] if args.backend == "nccl" else np.float32)
+              for i, (r, d) in enumerate(zip(rows, dims))]
+    B = args.batch
+    values, offsets = [], []
+    for i, r in enumerate(rows):
+        lens = rng.integers(0, 6, B) if i % 3 else np.ones(B, dtype=np.int64)
+        o = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+        offsets.append(o)
+        values.append(rng.integers(0, r, o[-1]).astype(np.int32))
+    table_bytes = [t.nbytes for t in tables]
+    traffic = [float(o[-1]) * t.shape[1] * t.itemsize for o, t in zip(offsets, tables)]
+    owner = plan_shards(table_bytes, traffic, world)
+    summ = shard_summary(owner, table_bytes, traffic, world)
+    assert sorted(set(owner)) == list(range(world)), owner
+    local = [f for f, r in enumerate(owner) if r == rank]
+
+    if args.backend == "nccl":
+        mod = ShardedFeatEmbed(rank, world, owner, dims, local_tables=[torch.from_numpy(tables[f]).to(dev) for f in local],
+                               device=dev, chunks=args.chunks)
+        lv = [torch.from_numpy(values[f]).to(dev) for f in local]
+        lo = [torch.from_numpy(offsets[f]).to(dev) for f in local]
+    else:
+        def pool_fn(vals, offs, out):
+            res = oracle.pool([tables[f] for f in local], [v.numpy() for v in vals], [o.numpy() for o in offs])
+            out[:, : res.shape[1]] = torch.from_numpy(res)
+
+        def place_fn(recv, out_k, nrows):
+            for so, sl, dc, w in mod.segments(nrows):
+                block = recv[so: so + (nrows - 1) * sl + w]
+                for rr in range(nrows):
+                    out_k[rr, dc: dc + w] = block[rr * sl: rr * sl + w]
+
+        mod = ShardedFeatEmbed(rank, world, owner, dims, chunks=args.chunks, pool_fn=pool_fn, place_fn=place_fn)
+        lv = [torch.from_numpy(values[f]) for f in local]
+        lo = [torch.from_numpy(offsets[f]) for f in local]
+    out = mod(lv, lo)
+    if args.backend == "nccl":
+        torch.cuda.synchronize()
+    expect = oracle.pool(tables, values, offsets, acc64=True)[local_sample_ids(B, world, args.chunks, rank)]
+    np.testing.assert_allclose(out.cpu().numpy(), expect, rtol=2e-3 if args.backend == "nccl" else 1e-5, atol=1e-5)
+    # a second call reuses the buffers
+    out2 = mod(lv, lo)
+    if args.backend == "nccl":
+        torch.cuda.synchronize()
+    assert torch.equal(out, out2)
+    dist.barrier()
+    if rank == 0:
+        print("sharded ok", args.backend, "world", world, "imbalance %.3f" % summ["traffic_imbalance"], flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
