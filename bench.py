@@ -59,6 +59,8 @@ def parse_args():
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--chunks", type=int, default=4, help="batch chunks of the sharded path (exchange/pooling overlap)")
+    p.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
+                   help="sharded path: fused peer-memory stores, or pool + NCCL all-to-all + placement")
     return p.parse_args()
 
 
@@ -408,7 +410,8 @@ def run_sharded(args):
     local = [f for f, r in enumerate(owner) if r == rank]
     tables = synth.make_tables_device(cfg, dev, features=local)
     dims = [fs.dim for fs in cfg.features]
-    mod = ShardedFeatEmbed(rank, world, owner, dims, local_tables=tables, device=dev, chunks=args.chunks)
+    mod = ShardedFeatEmbed(rank, world, owner, dims, local_tables=tables, device=dev, chunks=args.chunks,
+                           exchange=args.exchange)
     mod.set_batch_for_empty_rank(B)
     if mod.local is not None:
         mod.local.set_schedules(None, occupancy=args.occupancy or 6)
@@ -425,10 +428,14 @@ def run_sharded(args):
         host.append((hv, ho))
         devb.append(([t.to(dev) for t in hv], [t.to(dev) for t in ho]))
         alg.append(bytes_i)
-    out = torch.empty((B // world, cfg.output_units), dtype=torch.float32, device=dev)
     host_out = torch.empty((B // world, cfg.output_units), dtype=torch.float32).pin_memory()
+    if args.exchange == "peer":
+        run_step = lambda v, o: mod(v, o)
+    else:
+        out_buf = torch.empty((B // world, cfg.output_units), dtype=torch.float32, device=dev)
+        run_step = lambda v, o: mod(v, o, out=out_buf)
     for i in range(max(3, args.warmup)):
-        mod(*devb[i % nb], out=out)
+        out = run_step(*devb[i % nb])
     if mod.local is not None:
         mod.local.check_status()
 
@@ -441,7 +448,7 @@ def run_sharded(args):
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
     for i in range(K):
-        mod(*devb[i % nb], out=out)
+        run_step(*devb[i % nb])
     ev1.record()
     barrier()
     t_dev = ev0.elapsed_time(ev1) * 1e-3
@@ -455,8 +462,7 @@ def run_sharded(args):
             hv, ho = host[i % nb]
             dv = [t.to(dev, non_blocking=True) for t in hv]
             do = [t.to(dev, non_blocking=True) for t in ho]
-            mod(dv, do, out=out)
-            host_out.copy_(out, non_blocking=True)
+            host_out.copy_(run_step(dv, do), non_blocking=True)
 
         e2e_step(0)
         barrier()
@@ -469,7 +475,8 @@ def run_sharded(args):
         t_e2e = ev2.elapsed_time(ev3) * 1e-3
     sampler.stop()
 
-    k_sum = sum(ktimes) / max(1, min(K, 256 // args.chunks)) if ktimes else 0.0  # pooled-kernel ms per step on this rank
+    launches_per_step = 1 if args.exchange == "peer" else args.chunks
+    k_sum = sum(ktimes) / max(1, min(K, 256 // launches_per_step)) if ktimes else 0.0  # pooled-kernel ms per step, this rank
     stats = torch.tensor([t_dev, t_e2e or 0.0, k_sum, float(sum(alg) / len(alg))], dtype=torch.float64, device=dev)
     mx = stats.clone()
     dist.all_reduce(mx, op=dist.ReduceOp.MAX)
@@ -490,8 +497,11 @@ def run_sharded(args):
             "config": {"workload": cfg.name, "features": F, "global_batch": B, "table_dtype": cfg.features[0].dtype,
                        "table_gb_total": round(cfg.table_bytes / 1e9, 1), "output_units": cfg.output_units,
                        "partitioning": f"table-wise shards over {world} ranks (LPT planner, traffic imbalance "
-                                       f"{summ['traffic_imbalance']:.3f}), NCCL all-to-all of pooled fp32 rows in "
-                                       f"{args.chunks} chunks, column placement kernel",
+                                       f"{summ['traffic_imbalance']:.3f}); exchange: " +
+                                       ("pooled rows stored by the fused kernel into the destination rank's output "
+                                        "over NVLink peer memory, one-element all-reduce as the barrier"
+                                        if args.exchange == "peer" else
+                                        f"NCCL all-to-all of pooled fp32 rows in {args.chunks} chunks + placement kernel"),
                        "exchange_bytes_sent_per_rank_per_step": int(exch), "row_scale": args.row_scale,
                        "l2": f"inputs larger than L2: {max(summ['bytes_per_rank']) / 1e9:.0f} GB of tables per rank, "
                              f"{nb} distinct batches rotated", "occupancy": args.occupancy or 6},
@@ -503,11 +513,13 @@ def run_sharded(args):
             "e2e": {"value": K * B / t_e2e_m if t_e2e_m else None, "unit": UNIT, "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(B // world * cfg.output_units * 4),
                     "ms_per_step": t_e2e_m / K * 1e3 if t_e2e_m else None},
-            "gpu_launches": K * args.chunks * 3,
+            "gpu_launches": K * (2 if args.exchange == "peer" else args.chunks * 3),
             "clocks": sampler.summary(),
         }
         print(json.dumps(line), flush=True)
     dist.barrier()
+    if args.exchange == "peer":
+        mod.close()
     dist.destroy_process_group()
 
 

@@ -9,7 +9,8 @@
  *    failure.  No C++ exception crosses this boundary.
  *  - The caller owns every buffer.  The library allocates device memory only
  *    inside eb_create() (a descriptor table of a few KB per handle, released
- *    by eb_destroy()); all per-call scratch lives in the caller's `workspace`.
+ *    by eb_destroy()) and eb_peer_alloc(); all per-call scratch lives in the
+ *    caller's `workspace`.
  *  - Every launch goes to the `stream` argument (a cudaStream_t passed as
  *    void*, so that this header needs no CUDA include).
  *  - A handle is not thread-safe: use one handle per host thread / stream.
@@ -215,6 +216,48 @@ int eb_check_status(eb_handle* h, void* workspace, void* stream);
  */
 int eb_fill_table(void* table, int64_t rows, int32_t dim, int32_t table_dtype, uint64_t seed,
                   float std, int device, void* stream);
+
+/*
+ * Place the features' outputs at arbitrary columns: feature f writes columns
+ * [first_column[f], first_column[f] + dim_f) of an output row that is `units`
+ * wide (NULL restores the default, features side by side).  Used by the sharded
+ * path, where a rank's features go to their canonical columns of the global
+ * [batch, sum of all dims] layout.  No counterpart in the reference, whose
+ * column offsets are compile-time constants (d_embed_dim_offsets,
+ * RecFlex/code_emitter/codegen.py:287-292).
+ */
+int eb_set_output_columns(eb_handle* h, const int32_t* first_column, int64_t units);
+
+/*
+ * Fused pooling + exchange for table-wise sharding (no counterpart in the
+ * reference): like eb_forward, but sample b of the batch is stored into the
+ * output matrix of rank b / (batch / world), at row b % (batch / world).
+ * peer_out[r] is THIS process's device pointer to rank r's [batch / world,
+ * out_ld] fp32 matrix (its own for r == its rank, peers' through
+ * eb_peer_open), so the pooled rows cross NVLink as plain stores from the
+ * kernel that computes them and no all-to-all or re-layout pass follows.
+ * batch / world must be a multiple of 32, world <= 16.  The kernel never waits
+ * on another GPU; the caller orders consumers after ALL ranks' kernels (for
+ * example with an all-reduce on the same stream) and must not let a rank start
+ * step k + 2 into a buffer a peer may still be reading from step k.
+ */
+int eb_forward_peers(eb_handle* h, int64_t batch, const void* const* values_ptrs,
+                     const void* const* offsets_ptrs, const int64_t* nnz, int index_dtype,
+                     int offsets_have_end, float* const* peer_out, int world, int64_t out_ld,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Device buffers other processes of this node can map (CUDA IPC): eb_peer_alloc
+ * allocates `bytes` on `device` and fills a 64-byte handle to send to the other
+ * ranks; eb_peer_open maps a peer's handle into this process (the returned
+ * pointer is valid on `device`); eb_peer_close unmaps; eb_peer_free releases an
+ * eb_peer_alloc buffer.  These are the only other allocating calls besides
+ * eb_create.
+ */
+int eb_peer_alloc(int device, size_t bytes, void** ptr, unsigned char* handle64);
+int eb_peer_open(int device, const unsigned char* handle64, void** ptr);
+int eb_peer_close(int device, void* ptr);
+int eb_peer_free(int device, void* ptr);
 
 /*
  * Column placement for table-wise sharding (no counterpart in the reference,

@@ -72,6 +72,14 @@ PROTOTYPES = {
     "eb_check_status": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "eb_fill_table": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_uint64, C.c_float, C.c_int,
                                 C.c_void_p]),
+    "eb_set_output_columns": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_int64]),
+    "eb_forward_peers": (C.c_int, [C.c_void_p, C.c_int64, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
+                                   C.POINTER(C.c_int64), C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_int, C.c_int64,
+                                   C.c_void_p, C.c_size_t, C.c_void_p]),
+    "eb_peer_alloc": (C.c_int, [C.c_int, C.c_size_t, C.POINTER(C.c_void_p), C.c_void_p]),
+    "eb_peer_open": (C.c_int, [C.c_int, C.c_void_p, C.POINTER(C.c_void_p)]),
+    "eb_peer_close": (C.c_int, [C.c_int, C.c_void_p]),
+    "eb_peer_free": (C.c_int, [C.c_int, C.c_void_p]),
     "eb_place_columns": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_void_p, C.c_int,
                                    C.c_void_p]),
     "eb_parse_bags": (C.c_int, [C.c_char_p, C.c_size_t, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p,

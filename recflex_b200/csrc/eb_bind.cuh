@@ -147,6 +147,7 @@ __global__ void __launch_bounds__(kBindThreads) eb_bind_kernel(LaunchArgs a, int
     hdr->cta_tiles = 0;
     hdr->status = status;
   }
+  if (tid < kMaxPeers) hdr->peer_out[tid] = a.peer_out[tid];
 }
 
 // ---------------------------------------------------------------------------

@@ -323,6 +323,24 @@ int eb_set_schedules(eb_handle* h, const eb_schedule* per_feature, int occupancy
   return EB_OK;
 }
 
+int eb_set_output_columns(eb_handle* h, const int32_t* first_column, int64_t units) {
+  if (!h) return fail(EB_ERR_INVALID_ARG, "null handle");
+  if (!first_column) {  // back to the default: features side by side
+    int64_t col = 0;
+    for (auto& fs : h->feats) { fs.col_off = (int32_t)col; col += fs.dim; }
+    h->units = col;
+  } else {
+    for (int f = 0; f < h->num_features; ++f)
+      if (first_column[f] < 0 || (int64_t)first_column[f] + h->feats[f].dim > units)
+        return fail(EB_ERR_INVALID_ARG, "feature %d: columns [%d, %d) fall outside [0, %lld)", f, first_column[f],
+                    first_column[f] + h->feats[f].dim, (long long)units);
+    for (int f = 0; f < h->num_features; ++f) h->feats[f].col_off = first_column[f];
+    h->units = units;
+  }
+  DeviceGuard guard(h->device);
+  return upload_feats(h);
+}
+
 int eb_get_schedules(const eb_handle* h, eb_schedule* per_feature, int* occupancy) {
   if (!h) return fail(EB_ERR_INVALID_ARG, "null handle");
   if (per_feature)
@@ -360,6 +378,76 @@ int eb_forward(eb_handle* h, int64_t batch, const void* const* values_ptrs, cons
   if (rc != EB_OK) return rc;
   const LaunchArgs a = make_args(h, batch, index_dtype, offsets_have_end, out, out_ld, workspace);
   return run(h, a, false, st);
+}
+
+int eb_forward_peers(eb_handle* h, int64_t batch, const void* const* values_ptrs, const void* const* offsets_ptrs,
+                     const int64_t* nnz, int index_dtype, int offsets_have_end, float* const* peer_out, int world,
+                     int64_t out_ld, void* workspace, size_t workspace_bytes, void* stream) {
+  if (world < 1 || world > kMaxPeers) return fail(EB_ERR_INVALID_ARG, "world must be 1..%d (got %d)", kMaxPeers, world);
+  if (!peer_out) return fail(EB_ERR_INVALID_ARG, "null peer_out");
+  int rc = check_forward_common(h, batch, index_dtype, peer_out[0], out_ld, workspace, workspace_bytes);
+  if (rc != EB_OK) return rc;
+  if (batch == 0) return EB_OK;
+  if (batch % world != 0 || (batch / world) % 32 != 0)
+    return fail(EB_ERR_INVALID_ARG, "batch / world must be a whole multiple of 32 (batch %lld, world %d)",
+                (long long)batch, world);
+  bool vec = out_ld % 4 == 0;
+  for (int r = 0; r < world; ++r) {
+    if (!peer_out[r]) return fail(EB_ERR_INVALID_ARG, "null output pointer for rank %d", r);
+    if (reinterpret_cast<uintptr_t>(peer_out[r]) & 3) return fail(EB_ERR_INVALID_ARG, "rank %d: output not 4-byte aligned", r);
+    vec = vec && (reinterpret_cast<uintptr_t>(peer_out[r]) & 15) == 0;
+  }
+  DeviceGuard guard(h->device);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  rc = upload_dyn(h, batch, values_ptrs, offsets_ptrs, nnz, offsets_have_end, workspace, st);
+  if (rc != EB_OK) return rc;
+  LaunchArgs a = make_args(h, batch, index_dtype, offsets_have_end, peer_out[0], out_ld, workspace);
+  a.out_vec = vec;
+  a.rows_per_peer = batch / world;
+  for (int r = 0; r < world; ++r) a.peer_out[r] = peer_out[r];
+  return run(h, a, false, st);
+}
+
+int eb_peer_alloc(int device, size_t bytes, void** ptr, unsigned char* handle64) {
+  if (!ptr || !handle64 || bytes == 0) return fail(EB_ERR_INVALID_ARG, "invalid argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle is 64 bytes");
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(EB_ERR_CUDA, "cannot select device %d", device);
+  void* p = nullptr;
+  EB_CUDA(cudaMalloc(&p, bytes));
+  cudaIpcMemHandle_t hd;
+  cudaError_t e = cudaIpcGetMemHandle(&hd, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return fail(EB_ERR_CUDA, "cudaIpcGetMemHandle failed: %s", cudaGetErrorString(e));
+  }
+  memcpy(handle64, &hd, 64);
+  *ptr = p;
+  return EB_OK;
+}
+
+int eb_peer_open(int device, const unsigned char* handle64, void** ptr) {
+  if (!ptr || !handle64) return fail(EB_ERR_INVALID_ARG, "invalid argument");
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(EB_ERR_CUDA, "cannot select device %d", device);
+  cudaIpcMemHandle_t hd;
+  memcpy(&hd, handle64, 64);
+  EB_CUDA(cudaIpcOpenMemHandle(ptr, hd, cudaIpcMemLazyEnablePeerAccess));
+  return EB_OK;
+}
+
+int eb_peer_close(int device, void* ptr) {
+  if (!ptr) return EB_OK;
+  DeviceGuard guard(device);
+  EB_CUDA(cudaIpcCloseMemHandle(ptr));
+  return EB_OK;
+}
+
+int eb_peer_free(int device, void* ptr) {
+  if (!ptr) return EB_OK;
+  DeviceGuard guard(device);
+  EB_CUDA(cudaFree(ptr));
+  return EB_OK;
 }
 
 int eb_forward_packed(eb_handle* h, int64_t batch, const void* values, const void* offsets, int index_dtype,

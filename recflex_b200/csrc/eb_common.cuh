@@ -45,16 +45,19 @@ struct __align__(8) FeatDyn {
 };
 static_assert(sizeof(FeatDyn) == 32, "FeatDyn must stay 32 bytes");
 
-// First 128 bytes of the workspace.
+constexpr int kMaxPeers = 16;            // ranks whose output matrices one launch can store into
+
+// First 256 bytes of the workspace.
 struct __align__(128) WsHeader {
   uint32_t ticket;        // next warp tile
   uint32_t total_tiles;
-  uint32_t cta_ticket;    // next CTA tile (block-per-bag features)
+  uint32_t cta_ticket;    // next CTA tile (reserved)
   uint32_t cta_tiles;
   uint32_t status;
   uint32_t pad_[27];
+  float* peer_out[kMaxPeers];  // peer mode: output matrix of every rank (this GPU's view of their memory)
 };
-static_assert(sizeof(WsHeader) == 128, "WsHeader must stay 128 bytes");
+static_assert(sizeof(WsHeader) == 256, "WsHeader must stay 256 bytes");
 
 // Host/device view of where each array sits inside the workspace.
 struct WsLayout {
@@ -92,6 +95,9 @@ struct LaunchArgs {
   int32_t packed;
   int32_t out_vec;        // out base and out_ld allow 16-byte stores
   int32_t warps_total;    // persistent warps of the fused kernel (for tile sizing)
+  // peer mode (rows_per_peer > 0): sample b is stored to peer_out[b / rows_per_peer], row b % rows_per_peer
+  int64_t rows_per_peer;
+  float* peer_out[kMaxPeers];
 };
 
 }  // namespace ebk

@@ -104,6 +104,9 @@ __global__ void __launch_bounds__(kCtaThreads, OCC) eb_fused_kernel(LaunchArgs a
     ctx.batch = a.batch;
     ctx.out = a.out + fs.col_off;
     ctx.out_ld = a.out_ld;
+    ctx.peer_out = hdr->peer_out;
+    ctx.rows_per_peer = a.rows_per_peer;
+    ctx.col_off = fs.col_off;
     ctx.status = &hdr->status;
     ctx.dim = fs.dim;
     ctx.row_bytes = fs.row_bytes;

@@ -47,7 +47,7 @@ constexpr int kNoAllocOccupancy = 4;
 
 // descriptor table first, then a workspace laid out by ws_layout(kMaxFeat)
 constexpr size_t kDescBytes = sizeof(FeatStatic) * (size_t)kMaxFeat;
-constexpr size_t kWsBytesMax = 128 + 6 * 128 + (size_t)kMaxFeat * (4 + 4 + 4 + 4 + sizeof(FeatDyn) + 8) + 8;
+constexpr size_t kWsBytesMax = sizeof(WsHeader) + 6 * 128 + (size_t)kMaxFeat * (4 + 4 + 4 + 4 + sizeof(FeatDyn) + 8) + 8;
 constexpr size_t kNoAllocScratchBytes = kDescBytes + ((kWsBytesMax + 255) / 256) * 256;
 
 // The name below is a host-side stand-in for the device array: host code must

@@ -30,8 +30,11 @@ struct TileCtx {
   int64_t rows;
   int64_t nnz;
   int64_t batch;
-  float* out;        // already advanced to the feature's first column
+  float* out;        // already advanced to the feature's first column (unused in peer mode)
   int64_t out_ld;
+  float* const* peer_out;  // peer mode: every rank's output matrix
+  int64_t rows_per_peer;   // 0 = single output matrix
+  int32_t col_off;
   uint32_t* status;
   int32_t dim;
   int32_t row_bytes;
@@ -45,6 +48,15 @@ struct TileCtx {
 __device__ __forceinline__ int64_t load_index(const char* base, int64_t i, bool idx64) {
   return idx64 ? (int64_t)__ldg(reinterpret_cast<const long long*>(base) + i)
                : (int64_t)__ldg(reinterpret_cast<const int*>(base) + i);
+}
+
+// First output element (this feature's first column) of bag `bb`.  In peer mode
+// the bag's row lives in the output matrix of rank bb / rows_per_peer; chunks of
+// 32 bags never straddle two ranks because rows_per_peer is a multiple of 32.
+__device__ __forceinline__ float* chunk_out(const TileCtx& c, int64_t bb) {
+  if (c.rows_per_peer == 0) return c.out + bb * c.out_ld;
+  const int64_t d = bb / c.rows_per_peer;
+  return c.peer_out[d] + c.col_off + (bb - d * c.rows_per_peer) * c.out_ld;
 }
 
 __device__ __forceinline__ void flag(uint32_t* status, uint32_t bit) {
@@ -237,10 +249,10 @@ __device__ __forceinline__ void tile_group(const TileCtx& c, int64_t b0, int64_t
     const int cs = (xc * G + cl) * V;
     const bool col_ok = cs < c.dim;
     const char* tcol = c.table + (size_t)cs * sizeof(T);
-    float* ocol = c.out + cs;
     for (int64_t bb = b0; bb < b1; bb += 32) {
       const int nb = (int)((b1 - bb) < 32 ? (b1 - bb) : 32);
       const Chunk ch = load_chunk(c, bb, nb, lane);
+      float* orow = chunk_out(c, bb) + cs;
       const typename IdxOf<IDX64>::type* vals = reinterpret_cast<const typename IdxOf<IDX64>::type*>(c.values) + ch.e0;
       for (int i0 = 0; i0 < nb; i0 += R) {
         const int bi = i0 + r;
@@ -263,7 +275,7 @@ __device__ __forceinline__ void tile_group(const TileCtx& c, int64_t b0, int64_t
 #pragma unroll
           for (int u = 0; u < U; ++u) Ops::add(acc, rows[u]);
         }
-        if (bi < nb && col_ok) store_vals<V>(ocol + (bb + bi) * c.out_ld, acc, c.out_vec);
+        if (bi < nb && col_ok) store_vals<V>(orow + (int64_t)bi * c.out_ld, acc, c.out_vec);
       }
     }
   }
@@ -281,10 +293,10 @@ __device__ __forceinline__ void tile_warp(const TileCtx& c, int64_t b0, int64_t 
     const int cs = (xc * G + cl) * V;
     const bool col_ok = cs < c.dim;
     const char* tcol = c.table + (size_t)cs * sizeof(T);
-    float* ocol = c.out + cs;
     for (int64_t bb = b0; bb < b1; bb += 32) {
       const int nb = (int)((b1 - bb) < 32 ? (b1 - bb) : 32);
       const Chunk ch = load_chunk(c, bb, nb, lane);
+      float* orow = chunk_out(c, bb) + cs;
       const typename IdxOf<IDX64>::type* vals = reinterpret_cast<const typename IdxOf<IDX64>::type*>(c.values) + ch.e0;
       for (int i = 0; i < nb; ++i) {
         const int s = __shfl_sync(kFull, ch.lo, i);
@@ -311,7 +323,7 @@ __device__ __forceinline__ void tile_warp(const TileCtx& c, int64_t b0, int64_t 
             for (int k = 0; k < V; ++k) acc[k] += __shfl_xor_sync(kFull, acc[k], d);
           }
         }
-        if (r == 0 && col_ok) store_vals<V>(ocol + (bb + i) * c.out_ld, acc, c.out_vec);
+        if (r == 0 && col_ok) store_vals<V>(orow + (int64_t)i * c.out_ld, acc, c.out_vec);
       }
     }
   }
@@ -335,14 +347,13 @@ __device__ __forceinline__ void tile_flat(const TileCtx& c, int64_t b0, int64_t 
     const int cs = (xc * G + cl) * V;
     const bool col_ok = cs < c.dim;
     const char* tcol = c.table + (size_t)cs * sizeof(T);
-    float* ocol = c.out + cs;
     for (int64_t bb = b0; bb < b1; bb += 32) {
       const int nb = (int)((b1 - bb) < 32 ? (b1 - bb) : 32);
       const Chunk ch = load_chunk(c, bb, nb, lane);
+      float* orow = chunk_out(c, bb) + cs;
       const typename IdxOf<IDX64>::type* vals = reinterpret_cast<const typename IdxOf<IDX64>::type*>(c.values) + ch.e0;
       const int n = ch.n;
       const bool nonempty = ch.hi > ch.lo;
-      float* orow = ocol + bb * c.out_ld;
 
       // empty bags pool to zero
       {
@@ -477,12 +488,11 @@ __device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_
     const int cs = (xc * G + cl) * V;
     const bool col_ok = cs < c.dim;
     const char* tcol = c.table + (size_t)cs * sizeof(T);
-    float* ocol = c.out + cs;
     for (int64_t bb = b0; bb < b1; bb += 32) {
       const int nb = (int)((b1 - bb) < 32 ? (b1 - bb) : 32);
       const Chunk ch = load_chunk(c, bb, nb, lane);
       const int n = ch.n;
-      float* orow = ocol + bb * c.out_ld;
+      float* orow = chunk_out(c, bb) + cs;
       const unsigned nz = __ballot_sync(kFull, ch.hi > ch.lo);
 
       // empty bags pool to zero: slot r takes the r-th remaining one

@@ -212,6 +212,42 @@ class FeatEmbed(nn.Module):
         times = torch.tensor([ns[f] * 1e-6 for f in range(n_t)], dtype=torch.float64)
         return out, times
 
+    def set_output_columns(self, first_column: Optional[Sequence[int]], units: int = 0) -> None:
+        """Feature f writes columns [first_column[f], first_column[f] + dim_f) of a `units`-wide output row
+        (None restores the default side-by-side layout)."""
+        if first_column is None:
+            _lib.check(self._lib.eb_set_output_columns(self._h, None, 0))
+            self.output_units = sum(int(t.shape[1]) for t in self.embed_tables)
+            return
+        if len(first_column) != self.num_features:
+            raise ValueError(f"{len(first_column)} columns for {self.num_features} features")
+        arr = (C.c_int32 * self.num_features)(*[int(c) for c in first_column])
+        _lib.check(self._lib.eb_set_output_columns(self._h, arr, int(units)))
+        self.output_units = int(units)
+
+    def forward_peers(self, values: Sequence[torch.Tensor], offsets: Sequence[torch.Tensor],
+                      peer_ptrs: Sequence[int], out_ld: int) -> None:
+        """Fused pooling + exchange: sample b goes to the output matrix of rank b // (batch / world) whose
+        device pointer (as seen from this process) is peer_ptrs[rank].  offsets carry batch + 1 entries."""
+        F, W = self.num_features, len(peer_ptrs)
+        idt = self._index_dtype(values[0])
+        batch = offsets[0].numel() - 1
+        vp = (C.c_void_p * F)()
+        op = (C.c_void_p * F)()
+        nnz = (C.c_int64 * F)()
+        for f in range(F):
+            v, o = values[f], offsets[f]
+            if self._index_dtype(v) != idt or self._index_dtype(o) != idt:
+                raise TypeError("all values and offsets tensors must share one integer dtype")
+            if o.numel() != batch + 1 or not v.is_contiguous() or not o.is_contiguous():
+                raise ValueError(f"feature {f}: offsets need batch + 1 entries; tensors must be contiguous")
+            if v.device != self.device or o.device != self.device:
+                raise ValueError(f"feature {f}: values/offsets must live on {self.device}")
+            vp[f], op[f], nnz[f] = v.data_ptr(), o.data_ptr(), v.numel()
+        pp = (C.c_void_p * W)(*[int(p) for p in peer_ptrs])
+        _lib.check(self._lib.eb_forward_peers(self._h, batch, vp, op, nnz, idt, 1, pp, W, int(out_ld),
+                                              C.c_void_p(self._ws_ptr), self._ws_bytes, self._stream()))
+
     def forward_packed(self, values: torch.Tensor, offsets: torch.Tensor, out: Optional[torch.Tensor] = None):
         """Same forward for one packed batch: `values` = all features' indices back to back,
         `offsets` = `[num_features, batch + 1]`, both on the device."""

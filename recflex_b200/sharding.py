@@ -11,7 +11,14 @@ RecFlex/tuning/measure.py:27,68); both modes here are new:
   every feature's columns at its canonical position, so that rank r ends with `[B / world, sum(dim)]` for
   its share of the samples, identical to what the unsharded module computes for those samples.
 
-Batch chunks pipeline the exchange behind the pooling: chunk k's all-to-all runs on a side stream
+Two exchanges are implemented.  `exchange="peer"` (default on GPUs) is the fused one: the outputs of all ranks
+live in buffers every rank has mapped (CUDA IPC over NVLink), and the fused kernel stores each pooled row straight
+into the destination rank's final matrix at the feature's canonical columns, so the transfer overlaps the pooling
+tile by tile and no send buffer, all-to-all or placement pass exists; a one-element all-reduce on the same stream
+tells every rank that all kernels are done.  `exchange="nccl"` is the library baseline: pool into a send buffer,
+`all_to_all_single`, placement kernel.
+
+With `exchange="nccl"`, batch chunks pipeline the exchange behind the pooling: chunk k's all-to-all runs on a side stream
 while chunk k + 1 is pooled.  With C chunks, sample b of the batch belongs to chunk `b // (B / C)` and,
 inside the chunk, to rank `(b % (B / C)) // (B / (C * world))`; a rank's output rows are its samples in
 batch order.
@@ -116,7 +123,7 @@ class ShardedFeatEmbed:
 
     def __init__(self, rank: int, world: int, owner: Sequence[int], dims: Sequence[int],
                  local_tables: Optional[List[torch.Tensor]] = None, device=None, group=None, chunks: int = 4,
-                 pool_fn: Optional[Callable] = None, place_fn: Optional[Callable] = None):
+                 pool_fn: Optional[Callable] = None, place_fn: Optional[Callable] = None, exchange: str = "nccl"):
         if len(owner) != len(dims):
             raise ValueError("owner and dims must have one entry per feature")
         self.rank, self.world, self.group = rank, world, group
@@ -150,6 +157,13 @@ class ShardedFeatEmbed:
             self.device = torch.device(device) if device is not None else torch.device("cpu")
         self._segs = {}      # rows per chunk -> device descriptor tensor for the placement kernel
         self._bufs = {}
+        if exchange not in ("nccl", "peer"):
+            raise ValueError("exchange must be 'nccl' or 'peer'")
+        if exchange == "peer" and pool_fn is not None:
+            raise ValueError("the peer exchange exists only on GPUs")
+        self.exchange = exchange
+        self._peer = None    # (batch, own pointers, per-buffer pointer lists, output views, mapped peer pointers)
+        self._step = 0
 
     # -- layout ------------------------------------------------------------
     def segments(self, rows: int) -> List[Tuple[int, int, int, int]]:
@@ -191,6 +205,8 @@ class ShardedFeatEmbed:
             batch = offsets[0].numel() - 1
         else:
             batch = self._empty_rank_batch
+        if self.exchange == "peer":
+            return self._forward_peer(values, offsets, batch)
         if batch % (W * Cn) != 0:
             raise ValueError(f"batch {batch} must be a multiple of world * chunks = {W * Cn}")
         bc = batch // Cn          # samples per chunk
@@ -240,6 +256,72 @@ class ShardedFeatEmbed:
         return out
 
     __call__ = forward
+
+    # -- fused exchange over peer memory -------------------------------------
+    def _setup_peer(self, batch: int):
+        W = self.world
+        if batch % W or (batch // W) % 32:
+            raise ValueError(f"peer exchange needs batch / world to be a multiple of 32 (batch {batch}, world {W})")
+        rows = batch // W
+        nbytes = rows * self.units * 4
+        own, handles = [], torch.empty((2, 64), dtype=torch.uint8)
+        for b in range(2):
+            ptr = C.c_void_p()
+            hbuf = (C.c_ubyte * 64)()
+            _lib.check(self._lib.eb_peer_alloc(self.device.index, nbytes, C.byref(ptr), hbuf))
+            own.append(int(ptr.value))
+            handles[b] = torch.tensor(list(hbuf), dtype=torch.uint8)
+        gathered = [torch.empty((2, 64), dtype=torch.uint8, device=self.device) for _ in range(W)]
+        dist.all_gather(gathered, handles.to(self.device), group=self.group)
+        ptrs, mapped = [[0] * W for _ in range(2)], []
+        for r in range(W):
+            hs = gathered[r].cpu()
+            for b in range(2):
+                if r == self.rank:
+                    ptrs[b][r] = own[b]
+                else:
+                    raw = (C.c_ubyte * 64)(*hs[b].tolist())
+                    p = C.c_void_p()
+                    _lib.check(self._lib.eb_peer_open(self.device.index, raw, C.byref(p)))
+                    ptrs[b][r] = int(p.value)
+                    mapped.append(int(p.value))
+
+        class _View:  # torch view of a library-owned buffer
+            def __init__(self, ptr):
+                self.__cuda_array_interface__ = {"shape": (rows, units), "typestr": "<f4", "data": (ptr, False),
+                                                 "version": 2}
+
+        units = self.units
+        views = [torch.as_tensor(_View(p), device=self.device) for p in own]
+        if self.local is not None:
+            self.local.set_output_columns([self.col_of[f] for f in self.local_features], self.units)
+        self._flag = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self._peer = (batch, own, ptrs, views, mapped)
+
+    def _forward_peer(self, values, offsets, batch: int) -> torch.Tensor:
+        if self._peer is None or self._peer[0] != batch:
+            self.close()
+            self._setup_peer(batch)
+        _, _, ptrs, views, _ = self._peer
+        b = self._step % 2
+        self._step += 1
+        if self.local is not None:
+            self.local.forward_peers(values, offsets, ptrs[b], self.units)
+        dist.all_reduce(self._flag, group=self.group)  # every rank's stores into my buffer are complete after this
+        return views[b]
+
+    def close(self) -> None:
+        """Unmap peers' buffers and free this rank's (call on every rank, after a barrier)."""
+        if self._peer is not None:
+            _, own, _, views, mapped = self._peer
+            del views
+            torch.cuda.synchronize(self.device)
+            for p in mapped:
+                self._lib.eb_peer_close(self.device.index, C.c_void_p(p))
+            dist.barrier(group=self.group)  # nobody still maps my buffers when I free them
+            for p in own:
+                self._lib.eb_peer_free(self.device.index, C.c_void_p(p))
+            self._peer = None
 
     _empty_rank_batch = 0
 

@@ -27,6 +27,7 @@ def main():
     ap.add_argument("--backend", default="gloo")
     ap.add_argument("--chunks", type=int, default=3)
     ap.add_argument("--batch", type=int, default=48)
+    ap.add_argument("--exchange", default="nccl")
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     if args.backend == "nccl":
@@ -59,7 +60,7 @@ def main():
 
     if args.backend == "nccl":
         mod = ShardedFeatEmbed(rank, world, owner, dims, local_tables=[torch.from_numpy(tables[f]).to(dev) for f in local],
-                               device=dev, chunks=args.chunks)
+                               device=dev, chunks=args.chunks, exchange=args.exchange)
         lv = [torch.from_numpy(values[f]).to(dev) for f in local]
         lo = [torch.from_numpy(offsets[f]).to(dev) for f in local]
     else:
@@ -79,14 +80,19 @@ def main():
     out = mod(lv, lo)
     if args.backend == "nccl":
         torch.cuda.synchronize()
-    expect = oracle.pool(tables, values, offsets, acc64=True)[local_sample_ids(B, world, args.chunks, rank)]
+    chunks_eff = 1 if args.exchange == "peer" else args.chunks  # the peer exchange splits the batch contiguously
+    expect = oracle.pool(tables, values, offsets, acc64=True)[local_sample_ids(B, world, chunks_eff, rank)]
     np.testing.assert_allclose(out.cpu().numpy(), expect, rtol=2e-3 if args.backend == "nccl" else 1e-5, atol=1e-5)
     # a second call reuses the buffers
     out2 = mod(lv, lo)
     if args.backend == "nccl":
         torch.cuda.synchronize()
     assert torch.equal(out, out2)
+    out3 = mod(lv, lo)  # peer exchange: a third call is back on the first of its two buffers
+    assert torch.equal(out3, out2)
     dist.barrier()
+    if args.backend == "nccl":
+        mod.close()
     if rank == 0:
         print("sharded ok", args.backend, "world", world, "imbalance %.3f" % summ["traffic_imbalance"], flush=True)
     dist.destroy_process_group()
