@@ -157,7 +157,9 @@ LaunchArgs make_args(const eb_handle* h, int64_t batch, int index_dtype, int has
   a.idx64 = index_dtype == EB_I64;
   a.has_end = has_end != 0;
   a.packed = 0;
-  a.out_vec = ((reinterpret_cast<uintptr_t>(out) & 15) == 0) && (out_ld % 4 == 0);
+  a.out_vec = ((reinterpret_cast<uintptr_t>(out) & 31) == 0 && out_ld % 8 == 0)
+                  ? 2
+                  : (((reinterpret_cast<uintptr_t>(out) & 15) == 0 && out_ld % 4 == 0) ? 1 : 0);
   a.warps_total = h->sm_count * h->occupancy * kWarpsPerCta;
   return a;
 }
@@ -391,11 +393,13 @@ int eb_forward_peers(eb_handle* h, int64_t batch, const void* const* values_ptrs
   if (batch % world != 0 || (batch / world) % 32 != 0)
     return fail(EB_ERR_INVALID_ARG, "batch / world must be a whole multiple of 32 (batch %lld, world %d)",
                 (long long)batch, world);
-  bool vec = out_ld % 4 == 0;
+  int vec = out_ld % 8 == 0 ? 2 : (out_ld % 4 == 0 ? 1 : 0);
   for (int r = 0; r < world; ++r) {
     if (!peer_out[r]) return fail(EB_ERR_INVALID_ARG, "null output pointer for rank %d", r);
-    if (reinterpret_cast<uintptr_t>(peer_out[r]) & 3) return fail(EB_ERR_INVALID_ARG, "rank %d: output not 4-byte aligned", r);
-    vec = vec && (reinterpret_cast<uintptr_t>(peer_out[r]) & 15) == 0;
+    const uintptr_t p = reinterpret_cast<uintptr_t>(peer_out[r]);
+    if (p & 3) return fail(EB_ERR_INVALID_ARG, "rank %d: output not 4-byte aligned", r);
+    if (vec == 2 && (p & 31)) vec = 1;
+    if (vec == 1 && (p & 15)) vec = 0;
   }
   DeviceGuard guard(h->device);
   cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -93,7 +93,7 @@ struct LaunchArgs {
   int32_t idx64;          // values/offsets are int64 (else int32)
   int32_t has_end;        // offsets carry batch + 1 entries
   int32_t packed;
-  int32_t out_vec;        // out base and out_ld allow 16-byte stores
+  int32_t out_vec;        // out base and out_ld allow 16-byte (1) or 32-byte (2) stores
   int32_t warps_total;    // persistent warps of the fused kernel (for tile sizing)
   // peer mode (rows_per_peer > 0): sample b is stored to peer_out[b / rows_per_peer], row b % rows_per_peer
   int64_t rows_per_peer;

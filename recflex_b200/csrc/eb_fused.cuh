@@ -114,7 +114,7 @@ __global__ void __launch_bounds__(kCtaThreads, OCC) eb_fused_kernel(LaunchArgs a
     ctx.nx = fs.nx;
     ctx.idx64 = a.idx64 != 0;
     ctx.has_end = a.has_end != 0;
-    ctx.out_vec = a.out_vec != 0 && (fs.col_off & 3) == 0;
+    ctx.out_vec = (a.out_vec == 2 && (fs.col_off & 7) == 0) ? 2 : ((a.out_vec != 0 && (fs.col_off & 3) == 0) ? 1 : 0);
 
     long long c0 = 0;
     if (TIMING) c0 = clock64();

@@ -172,7 +172,9 @@ int eb_forward_packed_noalloc(int device, int num_features, const int64_t* rows,
     a.idx64 = index_dtype == EB_I64;
     a.has_end = 1;
     a.packed = 1;
-    a.out_vec = ((reinterpret_cast<uintptr_t>(out) & 15) == 0) && (out_ld % 4 == 0);
+    a.out_vec = ((reinterpret_cast<uintptr_t>(out) & 31) == 0 && out_ld % 8 == 0)
+                    ? 2
+                    : (((reinterpret_cast<uintptr_t>(out) & 15) == 0 && out_ld % 4 == 0) ? 1 : 0);
     a.warps_total = g_sm_count[device] * kNoAllocOccupancy * kWarpsPerCta;
     e = launch_bind(a, false, st);
     if (e != cudaSuccess) { rc = fail(EB_ERR_CUDA, "bind launch failed: %s", cudaGetErrorString(e)); break; }

@@ -42,7 +42,7 @@ struct TileCtx {
   int32_t nx;
   bool idx64;
   bool has_end;
-  bool out_vec;
+  int out_vec;       // widest aligned store the output allows: 0 = scalar, 1 = 16 bytes, 2 = 32 bytes
 };
 
 __device__ __forceinline__ int64_t load_index(const char* base, int64_t i, bool idx64) {
@@ -126,11 +126,23 @@ struct RowOps<__half, 1> {
 
 // Streaming (evict-first) stores: the output is written once and never re-read
 // by this kernel, so it should not displace table rows from L2.
+// A lane that owns 8 floats writes them with ONE 32-byte store when alignment
+// allows: two 16-byte stores would each cover only half of every 32-byte
+// sector, which L2 merges for local memory but which crosses NVLink as
+// half-filled packets when the destination is a peer's memory.
 template <int V>
-__device__ __forceinline__ void store_vals(float* dst, const float (&a)[V], bool vec_ok) {
+__device__ __forceinline__ void store_vals(float* dst, const float (&a)[V], int vec_ok) {
   if constexpr (V == 1) {
     __stcs(dst, a[0]);
   } else {
+    if constexpr (V == 8) {
+      if (vec_ok == 2) {
+        asm volatile("st.global.cs.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "f"(a[0]), "f"(a[1]),
+                     "f"(a[2]), "f"(a[3]), "f"(a[4]), "f"(a[5]), "f"(a[6]), "f"(a[7])
+                     : "memory");
+        return;
+      }
+    }
     if (vec_ok) {
 #pragma unroll
       for (int k = 0; k < V; k += 4)
