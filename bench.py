@@ -59,6 +59,7 @@ def parse_args():
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--chunks", type=int, default=4, help="batch chunks of the sharded path (exchange/pooling overlap)")
+    p.add_argument("--tune", action="store_true", help="run the two-stage tuner on the first batch before timing (untimed)")
     p.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
                    help="sharded path: fused peer-memory stores, or pool + NCCL all-to-all + placement")
     return p.parse_args()
@@ -415,6 +416,7 @@ def run_sharded(args):
     mod.set_batch_for_empty_rank(B)
     if mod.local is not None:
         mod.local.set_schedules(None, occupancy=args.occupancy or 6)
+    tuned_note = "library defaults"
 
     nb = args.batches
     host, devb, alg = [], [], []
@@ -428,6 +430,11 @@ def run_sharded(args):
         host.append((hv, ho))
         devb.append(([t.to(dev) for t in hv], [t.to(dev) for t in ho]))
         alg.append(bytes_i)
+    if args.tune and mod.local is not None:
+        from recflex_b200.tuning import TuneConfig, Tuner
+
+        res = Tuner(mod.local, [devb[0]], TuneConfig(occupancies=(4, 5, 6, 8), reps=1, global_reps=2)).tune()
+        tuned_note = f"tuned per rank before timing (rank 0: occupancy {res.occupancy})"
     host_out = torch.empty((B // world, cfg.output_units), dtype=torch.float32).pin_memory()
     if args.exchange == "peer":
         run_step = lambda v, o: mod(v, o)
@@ -504,7 +511,7 @@ def run_sharded(args):
                                         f"NCCL all-to-all of pooled fp32 rows in {args.chunks} chunks + placement kernel"),
                        "exchange_bytes_sent_per_rank_per_step": int(exch), "row_scale": args.row_scale,
                        "l2": f"inputs larger than L2: {max(summ['bytes_per_rank']) / 1e9:.0f} GB of tables per rank, "
-                             f"{nb} distinct batches rotated", "occupancy": args.occupancy or 6},
+                             f"{nb} distinct batches rotated", "schedules": tuned_note},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak if achieved else None, "traffic": None, "kernel": "eb_fused_kernel",
                          "kernel_ms": k_max, "algorithmic_bytes_per_launch": total_alg / world,
