@@ -15,7 +15,8 @@ after `bash oracle/build_ref.sh`:
   num_blocks) that the reference's compiled host parsers return for them
   (ws::StringSplitToInt, examples/csrc/warp_per_sample_preprocess.cu:6-38;
   onehot::OneHotMultiBlock, examples/csrc/onehot_preprocess.cu:17-27), called
-  through oracle/_ref/libref_host.so.
+  through oracle/_ref/libref_host.so; plus a tiny model directory in the reference's text formats and what the
+  reference's readers (RecFlex/parser.py: parse_table_shapes, parse_raw_data_batches) return for it.
 
 The fixtures are committed; the tests never read the reference checkout.
 """
@@ -119,8 +120,34 @@ def main():
     n = lib.ref_onehot_parse(text, C.c_int64(len(text)), C.c_int64(len(onehot_lines)), 592, 256,
                              vals.ctypes.data_as(C.c_void_p), C.byref(tiles), C.byref(blocks))
     onehot = {"lines": onehot_lines, "indices": vals[:n].tolist(), "num_tiles": tiles.value, "num_blocks": blocks.value}
+    # the reference's text-format readers (RecFlex/parser.py) on a tiny generated model directory
+    import tempfile
+
+    from RecFlex.parser import parse_raw_data_batches, parse_table_shapes
+
+    frng = np.random.default_rng(99)
+    batch_sizes = [int(x) for x in frng.integers(1, 6, 9)]
+    files = {"batch_sizes.txt": "\n".join(map(str, batch_sizes)) + "\n", "table_config.txt": "100,16\n57,8\n300,32\n"}
+    for i, rows in enumerate([100, 57, 300]):
+        lines = []
+        for _ in range(sum(batch_sizes)):
+            n = int(frng.integers(0, 4))
+            lines.append(",".join(str(int(x)) for x in frng.integers(0, rows, n)))
+        files[f"f{i}.txt"] = "\n".join(lines) + "\n"
+    with tempfile.TemporaryDirectory() as d:
+        for name, text in files.items():
+            with open(os.path.join(d, name), "w") as f:
+                f.write(text)
+        fnames = [os.path.join(d, f"f{i}.txt") for i in range(3)]
+        formats = {
+            "files": files,
+            "table_shapes": [list(t) for t in parse_table_shapes(os.path.join(d, "table_config.txt"))],
+            "feat_major": parse_raw_data_batches(os.path.join(d, "batch_sizes.txt"), fnames, 4, seed=3),
+            "batch_major": parse_raw_data_batches(os.path.join(d, "batch_sizes.txt"), fnames, 4, seed=3,
+                                                  feat_major=False),
+        }
     with open(os.path.join(HERE, "parse_golden.json"), "w") as f:
-        json.dump({"ws": parsed, "onehot": onehot}, f, indent=1)
+        json.dump({"ws": parsed, "onehot": onehot, "formats": formats}, f, indent=1)
     print("wrote", os.listdir(HERE))
 
 

@@ -201,3 +201,29 @@ def test_synthetic_table_fill_is_bit_reproducible_on_cpu():
     cfg = synth.make_config(1, row_scale=0.01)
     for fs, t in zip(cfg.features, synth.make_tables_device(cfg, "cuda:0")):
         assert np.array_equal(t.cpu().numpy(), synth.synth_table(fs.seed, fs.rows, fs.dim, fs.dtype))
+
+
+def test_cuda_graph_capture_and_replay(cfg1):
+    """The packed forward is two launches with no host round-trip: it can be captured once and replayed on new
+    batches written into the same device buffers (the binding is recomputed on the device at every replay)."""
+    cfg, tables, values, offsets, mod = cfg1
+    mod.set_schedules(all_schedules("stream", 4, len(tables)), occupancy=4)
+    batches = [synth.gen_batch(cfg, seed) for seed in (3, 4, 5)]
+    packed = [synth.pack_batch(v, o) for v, o in batches]
+    cap = max(len(pv) for pv, _ in packed)
+    dv = torch.zeros(cap, dtype=torch.int32, device="cuda:0")
+    do = torch.zeros(packed[0][1].shape, dtype=torch.int32, device="cuda:0")
+    out = torch.empty((cfg.batch, mod.output_units), dtype=torch.float32, device="cuda:0")
+    dv[: len(packed[0][0])] = torch.from_numpy(packed[0][0]).cuda()
+    do.copy_(torch.from_numpy(packed[0][1]))
+    mod.forward_packed(dv, do, out=out)  # warm-up outside capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        mod.forward_packed(dv, do, out=out)
+    for (v, o), (pv, po) in zip(batches, packed):
+        dv[: len(pv)] = torch.from_numpy(pv).cuda()
+        do.copy_(torch.from_numpy(po))
+        graph.replay()
+        torch.cuda.synchronize()
+        check_against_oracle(out, tables, v, o, "f32")

@@ -87,3 +87,19 @@ def test_oracle_rejects_out_of_range_index():
         oracle.pool(t, [np.array([0, 4])], [np.array([0, 2])])
     out = oracle.pool(t, [np.array([0, 4])], [np.array([0, 2])], strict=False)
     assert np.all(out == 1.0)
+
+
+def test_text_format_readers_match_the_reference(tmp_path):
+    from recflex_b200 import parser
+
+    with open(os.path.join(GOLD, "parse_golden.json")) as f:
+        gold = json.load(f)["formats"]
+    for name, text in gold["files"].items():
+        (tmp_path / name).write_text(text)
+    fnames = [str(tmp_path / f"f{i}.txt") for i in range(3)]
+    assert [list(t) for t in parser.parse_table_shapes(str(tmp_path / "table_config.txt"))] == gold["table_shapes"]
+    assert parser.parse_raw_data_batches(str(tmp_path / "batch_sizes.txt"), fnames, 4, seed=3) == gold["feat_major"]
+    assert parser.parse_raw_data_batches(str(tmp_path / "batch_sizes.txt"), fnames, 4, seed=3,
+                                         feat_major=False) == gold["batch_major"]
+    (tmp_path / "schedule_config.txt").write_text("OneHotSchedule,OneHotMultiBlockSchedule\nWarpPerSampleSchedule,ReduceByKeySchedule,Nope\n")
+    assert parser.parse_schedule_types(str(tmp_path / "schedule_config.txt")) == [["group", "group"], ["group", "flat", None]]
