@@ -69,6 +69,13 @@ extern "C" {
  *                   balanced over indices like rbk:: and mbs::
  *                   (multi_block_per_sample_kernel.cuh:17-112) but with neither
  *                   atomics nor scans in the inner loop.
+ *   EB_SCHED_PIPE   EB_SCHED_STREAM with the rows in flight kept in a per-warp
+ *                   shared-memory ring filled by per-lane cp.async copies
+ *                   (unroll 2 / 4 / 8 -> 4 / 3 / 2 macro-steps deep) instead of
+ *                   in registers: more bytes in flight per lane, fewer
+ *                   registers; costs 64 KB of shared memory per CTA, so at most
+ *                   3 CTAs per SM run (a higher occupancy setting is honoured
+ *                   only up to what fits).  No counterpart in the reference.
  *   EB_SCHED_AUTO   let the library choose from dim, dtype and mean bag length.
  */
 #define EB_SCHED_AUTO 0
@@ -76,6 +83,7 @@ extern "C" {
 #define EB_SCHED_WARP 2
 #define EB_SCHED_FLAT 3
 #define EB_SCHED_STREAM 4
+#define EB_SCHED_PIPE 5
 
 typedef struct eb_handle eb_handle;
 

@@ -22,9 +22,9 @@ EB_ERR_TOO_LARGE = -6
 EB_F32, EB_F16 = 0, 1
 EB_I32, EB_I64 = 0, 1
 EB_NOALLOC_MAX_FEATURES = 1024
-EB_SCHED_AUTO, EB_SCHED_GROUP, EB_SCHED_WARP, EB_SCHED_FLAT, EB_SCHED_STREAM = 0, 1, 2, 3, 4
+EB_SCHED_AUTO, EB_SCHED_GROUP, EB_SCHED_WARP, EB_SCHED_FLAT, EB_SCHED_STREAM, EB_SCHED_PIPE = 0, 1, 2, 3, 4, 5
 SCHED_NAMES = {EB_SCHED_AUTO: "auto", EB_SCHED_GROUP: "group", EB_SCHED_WARP: "warp", EB_SCHED_FLAT: "flat",
-               EB_SCHED_STREAM: "stream"}
+               EB_SCHED_STREAM: "stream", EB_SCHED_PIPE: "pipe"}
 SCHED_KINDS = {v: k for k, v in SCHED_NAMES.items()}
 
 

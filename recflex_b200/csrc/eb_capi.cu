@@ -84,6 +84,7 @@ struct eb_handle {
   bool ev_used[kRing] = {};
   int ring_pos = 0;
   // optional event pairs around the fused-kernel launches
+  size_t smem_bytes = 0;   // dynamic shared memory of the fused kernel (the pipelined schedule's rings)
   bool time_kernels = false;
   std::vector<cudaEvent_t> t0, t1;
   int t_count = 0;
@@ -102,7 +103,7 @@ eb_schedule resolve(const eb_schedule& in) {
 }
 
 int check_schedule(const eb_schedule& s, int f) {
-  if (s.kind < EB_SCHED_AUTO || s.kind > EB_SCHED_STREAM)
+  if (s.kind < EB_SCHED_AUTO || s.kind > EB_SCHED_PIPE)
     return fail(EB_ERR_INVALID_ARG, "feature %d: unknown schedule kind %d", f, s.kind);
   if (!(s.unroll == 0 || s.unroll == 1 || s.unroll == 2 || s.unroll == 4 || s.unroll == 8))
     return fail(EB_ERR_INVALID_ARG, "feature %d: unroll must be 0, 1, 2, 4 or 8 (got %d)", f, s.unroll);
@@ -161,6 +162,7 @@ LaunchArgs make_args(const eb_handle* h, int64_t batch, int index_dtype, int has
                   ? 2
                   : (((reinterpret_cast<uintptr_t>(out) & 15) == 0 && out_ld % 4 == 0) ? 1 : 0);
   a.warps_total = h->sm_count * h->occupancy * kWarpsPerCta;
+  a.ring_bytes = (int32_t)(h->smem_bytes / kWarpsPerCta);
   return a;
 }
 
@@ -169,7 +171,7 @@ int run(eb_handle* h, const LaunchArgs& a, bool timing, cudaStream_t st) {
   EB_CUDA(launch_bind(a, timing, st));
   const bool rec = h->time_kernels && h->t_count < kTimeRing;
   if (rec) EB_CUDA(cudaEventRecord(h->t0[h->t_count], st));
-  EB_CUDA(launch_fused(a, h->occupancy, timing, h->sm_count * h->occupancy, st));
+  EB_CUDA(launch_fused(a, h->occupancy, timing, h->sm_count * h->occupancy, h->smem_bytes, st));
   if (rec) {
     EB_CUDA(cudaEventRecord(h->t1[h->t_count], st));
     ++h->t_count;
@@ -313,10 +315,19 @@ int eb_set_schedules(eb_handle* h, const eb_schedule* per_feature, int occupancy
       const int rc = check_schedule(per_feature[f], f);
       if (rc != EB_OK) return rc;
     }
+    int cells = 0;  // deepest ring any pipelined feature needs: unroll 2 -> 2 x 4, 4 -> 4 x 3, 8 -> 8 x 2
     for (int f = 0; f < h->num_features; ++f) {
       h->sched[f] = resolve(per_feature[f]);
+      // the ring holds 16-byte lane cells: element-wise fallback rows keep the register walk
+      if (h->sched[f].kind == EB_SCHED_PIPE && !h->feats[f].vec) h->sched[f].kind = EB_SCHED_STREAM;
       apply_schedule(h->feats[f], h->sched[f]);
+      if (h->sched[f].kind == EB_SCHED_PIPE) {
+        const int u = h->sched[f].unroll;
+        const int need = u <= 2 ? 8 : (u == 4 ? 12 : 16);
+        cells = need > cells ? need : cells;
+      }
     }
+    h->smem_bytes = (size_t)cells * kPipeCellBytes * kWarpsPerCta;
     DeviceGuard guard(h->device);
     const int rc = upload_feats(h);
     if (rc != EB_OK) return rc;
@@ -363,7 +374,7 @@ int eb_max_concurrent_ctas(const eb_handle* h, int occupancy, int* ctas) {
   const int occ = occupancy ? occupancy : h->occupancy;
   DeviceGuard guard(h->device);
   int per_sm = 0;
-  EB_CUDA(fused_ctas_per_sm(occ, &per_sm));
+  EB_CUDA(fused_ctas_per_sm(occ, h->smem_bytes, &per_sm));
   *ctas = h->sm_count * (per_sm < occ ? per_sm : occ);
   return EB_OK;
 }

@@ -12,6 +12,8 @@ constexpr int kCtaThreads = 256;        // one value for every feature, as in th
 constexpr int kWarpsPerCta = kCtaThreads / 32;
 constexpr int kMaxOccupancy = 8;        // 2048 threads per SM / 256
 constexpr int kBindThreads = 1024;
+constexpr int kPipeCellBytes = 512;      // one ring cell: 32 lanes x 16 bytes
+constexpr int kPipeMaxCells = 16;        // unroll x stages of the deepest pipelined variant
 constexpr int kMaxLptFeatures = 2048;   // features beyond this keep their input order
 
 // status bits written by the kernels (never a trap)
@@ -95,6 +97,8 @@ struct LaunchArgs {
   int32_t packed;
   int32_t out_vec;        // out base and out_ld allow 16-byte (1) or 32-byte (2) stores
   int32_t warps_total;    // persistent warps of the fused kernel (for tile sizing)
+  int32_t ring_bytes;     // shared memory per warp for the pipelined schedule's ring (0 when no feature uses it)
+  int32_t pad_;
   // peer mode (rows_per_peer > 0): sample b is stored to peer_out[b / rows_per_peer], row b % rows_per_peer
   int64_t rows_per_peer;
   float* peer_out[kMaxPeers];

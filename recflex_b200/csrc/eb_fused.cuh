@@ -27,6 +27,23 @@ namespace ebk {
     EB_DISPATCH_UNROLL(FN, float, 4, I64)                          \
   }
 
+// EB_SCHED_PIPE: ring depth is tied to the unroll so that a CTA needs 32 to 64 KB
+// of shared memory: unroll 2 -> 4 stages, 4 -> 3 stages, 8 -> 2 stages.
+#define EB_DISPATCH_PIPE_T(T, V, I64)                                                  \
+  switch (fs.unroll) {                                                                 \
+    case 1:                                                                            \
+    case 2: tile_stream<T, V, 2, I64, 4>(ctx, b0, b1, lane, ring); break;              \
+    case 4: tile_stream<T, V, 4, I64, 3>(ctx, b0, b1, lane, ring); break;              \
+    default: tile_stream<T, V, 8, I64, 2>(ctx, b0, b1, lane, ring); break;             \
+  }
+
+#define EB_DISPATCH_PIPE(I64)                                      \
+  if (fs.dtype == 1) {                                             \
+    EB_DISPATCH_PIPE_T(__half, 8, I64)                             \
+  } else {                                                         \
+    EB_DISPATCH_PIPE_T(float, 4, I64)                              \
+  }
+
 // 64-bit indices are the uncommon case: every schedule kind is instantiated for
 // them, but only at unroll 4 (the requested unroll is ignored).
 #define EB_DISPATCH_DTYPE_U4(FN, I64)                              \
@@ -43,8 +60,11 @@ namespace ebk {
     EB_DISPATCH_DTYPE_U4(tile_warp, true)                          \
   } else if (fs.kind == 3) {                                       \
     EB_DISPATCH_DTYPE_U4(tile_flat, true)                          \
-  } else {                                                         \
+  } else if (fs.kind == 4) {                                       \
     EB_DISPATCH_DTYPE_U4(tile_stream, true)                        \
+  } else {                                                         \
+    if (fs.dtype == 1) tile_stream<__half, 8, 4, true, 3>(ctx, b0, b1, lane, ring); \
+    else tile_stream<float, 4, 4, true, 3>(ctx, b0, b1, lane, ring); \
   }
 
 #define EB_DISPATCH_KIND(I64)                                      \
@@ -57,8 +77,10 @@ namespace ebk {
     EB_DISPATCH_DTYPE(tile_warp, I64)                              \
   } else if (fs.kind == 3) {                                       \
     EB_DISPATCH_DTYPE(tile_flat, I64)                              \
-  } else {                                                         \
+  } else if (fs.kind == 4) {                                       \
     EB_DISPATCH_DTYPE(tile_stream, I64)                            \
+  } else {                                                         \
+    EB_DISPATCH_PIPE(I64)                                          \
   }
 
 template <int OCC, bool TIMING>
@@ -73,6 +95,9 @@ __global__ void __launch_bounds__(kCtaThreads, OCC) eb_fused_kernel(LaunchArgs a
   const FeatDyn* dyn = reinterpret_cast<const FeatDyn*>(a.ws + L.dyn);
   unsigned long long* feat_ns = reinterpret_cast<unsigned long long*>(a.ws + L.feat_ns);
   const uint32_t total = hdr->total_tiles;
+  // per-warp ring of the pipelined schedule (a.ring_bytes per warp when any feature uses it, else none)
+  extern __shared__ __align__(16) unsigned char eb_smem[];
+  unsigned char* ring = eb_smem + (threadIdx.x >> 5) * a.ring_bytes;
 
   uint32_t t = 0;
   if (lane == 0) t = atomicAdd(&hdr->ticket, 1u);
@@ -138,6 +163,8 @@ __global__ void __launch_bounds__(kCtaThreads, OCC) eb_fused_kernel(LaunchArgs a
 #undef EB_DISPATCH_DTYPE
 #undef EB_DISPATCH_KIND
 #undef EB_DISPATCH_KIND64
+#undef EB_DISPATCH_PIPE
+#undef EB_DISPATCH_PIPE_T
 #undef EB_DISPATCH_DTYPE_U4
 
 }  // namespace ebk

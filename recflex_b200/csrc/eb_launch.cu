@@ -23,15 +23,33 @@ cudaError_t launch_bind(const LaunchArgs& a, bool zero_feature_times, cudaStream
   return cudaGetLastError();
 }
 
-cudaError_t launch_fused(const LaunchArgs& a, int occupancy, bool timing, int grid, cudaStream_t st) {
-  FusedKernel k = pick(occupancy, timing);
-  void* params[] = {const_cast<LaunchArgs*>(&a)};
-  return cudaLaunchKernel(reinterpret_cast<const void*>(k), dim3(grid), dim3(kCtaThreads), params, 0, st);
+// Dynamic shared memory above 48 KB must be opted into once per kernel function (and per device).
+static cudaError_t allow_smem(FusedKernel k, int occupancy, bool timing, size_t smem_bytes) {
+  static bool done[16][kMaxOccupancy + 1][2] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (smem_bytes <= 48 * 1024 || dev >= 16 || done[dev][occupancy][timing ? 1 : 0]) return cudaSuccess;
+  e = cudaFuncSetAttribute(reinterpret_cast<const void*>(k), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           kPipeMaxCells * kPipeCellBytes * kWarpsPerCta);
+  if (e == cudaSuccess) done[dev][occupancy][timing ? 1 : 0] = true;
+  return e;
 }
 
-cudaError_t fused_ctas_per_sm(int occupancy, int* per_sm) {
-  return cudaOccupancyMaxActiveBlocksPerMultiprocessor(per_sm, reinterpret_cast<const void*>(pick(occupancy, false)),
-                                                       kCtaThreads, 0);
+cudaError_t launch_fused(const LaunchArgs& a, int occupancy, bool timing, int grid, size_t smem_bytes, cudaStream_t st) {
+  FusedKernel k = pick(occupancy, timing);
+  cudaError_t e = allow_smem(k, occupancy, timing, smem_bytes);
+  if (e != cudaSuccess) return e;
+  void* params[] = {const_cast<LaunchArgs*>(&a)};
+  return cudaLaunchKernel(reinterpret_cast<const void*>(k), dim3(grid), dim3(kCtaThreads), params, smem_bytes, st);
+}
+
+cudaError_t fused_ctas_per_sm(int occupancy, size_t smem_bytes, int* per_sm) {
+  FusedKernel k = pick(occupancy, false);
+  cudaError_t e = allow_smem(k, occupancy, false, smem_bytes);
+  if (e != cudaSuccess) return e;
+  return cudaOccupancyMaxActiveBlocksPerMultiprocessor(per_sm, reinterpret_cast<const void*>(k), kCtaThreads,
+                                                       smem_bytes);
 }
 
 cudaError_t launch_fill(void* table, int64_t elems, int dtype, uint64_t seed, float std, cudaStream_t st) {

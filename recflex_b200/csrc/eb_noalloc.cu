@@ -178,7 +178,7 @@ int eb_forward_packed_noalloc(int device, int num_features, const int64_t* rows,
     a.warps_total = g_sm_count[device] * kNoAllocOccupancy * kWarpsPerCta;
     e = launch_bind(a, false, st);
     if (e != cudaSuccess) { rc = fail(EB_ERR_CUDA, "bind launch failed: %s", cudaGetErrorString(e)); break; }
-    e = launch_fused(a, kNoAllocOccupancy, false, g_sm_count[device] * kNoAllocOccupancy, st);
+    e = launch_fused(a, kNoAllocOccupancy, false, g_sm_count[device] * kNoAllocOccupancy, 0, st);
     if (e != cudaSuccess) { rc = fail(EB_ERR_CUDA, "fused launch failed: %s", cudaGetErrorString(e)); break; }
   } while (0);
   if (prev >= 0 && prev != device) cudaSetDevice(prev);

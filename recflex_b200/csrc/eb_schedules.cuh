@@ -480,6 +480,58 @@ __device__ __forceinline__ void tile_flat(const TileCtx& c, int64_t b0, int64_t 
 }
 
 // ---------------------------------------------------------------------------
+// cp.async primitives of the pipelined stream walk: each lane copies 16 bytes
+// global -> shared without passing through registers and later reads back only
+// its own cells, so no barrier is needed, only the per-thread group wait.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ unsigned smem_addr(const void* p) {
+  return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void cp_async16(unsigned dst, const void* src, unsigned src_bytes) {
+  // src_bytes = 0 reads nothing and fills the 16 destination bytes with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint4 lds16(unsigned addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+// Indices of the U entries starting at `first` (0 for entries at or past `limit`).
+template <int U, bool IDX64>
+__device__ __forceinline__ void load_indices(const typename IdxOf<IDX64>::type* vp, int first, int limit, bool col_ok,
+                                             typename IdxOf<IDX64>::type (&idx)[U]) {
+#pragma unroll
+  for (int u = 0; u < U; ++u) idx[u] = (col_ok && first + u < limit) ? __ldg(vp + first + u) : 0;
+}
+
+// Issue the copies of one macro-step (U entries starting at `first`) into ring cells dst + u * 512.
+template <typename T, int U, bool IDX64>
+__device__ __forceinline__ void issue_rows(const TileCtx& c, const char* tcol, bool col_ok,
+                                           const typename IdxOf<IDX64>::type (&idx)[U], int first, int limit,
+                                           unsigned dst) {
+  const unsigned rows32 = c.rows > 0x80000000ll ? 0x80000000u : (unsigned)c.rows;
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const bool ok = col_ok && first + u < limit;
+    bool valid;
+    const char* src;
+    if constexpr (IDX64) {
+      valid = (uint64_t)idx[u] < (uint64_t)c.rows;
+      src = tcol + (valid ? idx[u] : 0) * (int64_t)c.row_bytes;
+    } else {
+      valid = (unsigned)idx[u] < rows32;
+      src = tcol + (uint64_t)(valid ? (unsigned)idx[u] : 0u) * (unsigned)c.row_bytes;
+    }
+    if (ok && !valid) flag(c.status, kStatusBadIndex);
+    cp_async16(dst + u * 512, ok && valid ? src : c.table, ok && valid ? 16u : 0u);
+  }
+}
+
+// ---------------------------------------------------------------------------
 // EB_SCHED_STREAM: the chunk's n entries are cut into R contiguous pieces of
 // ceil(n / R) entries, one per slot.  Every slot walks its piece serially with
 // U rows in flight, whatever the bag lengths: a bag that ends inside the piece
@@ -490,8 +542,16 @@ __device__ __forceinline__ void tile_flat(const TileCtx& c, int64_t b0, int64_t 
 // accumulator and a head partial in the output row; after the walk a segmented
 // shuffle scan over the slots' tails patches each head (once per 32 bags).
 // ---------------------------------------------------------------------------
-template <typename T, int V, int U, bool IDX64>
-__device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_t b1, int lane) {
+//
+// D > 0 selects the pipelined form (EB_SCHED_PIPE): the rows in flight live in a
+// per-warp shared-memory ring of D macro-steps (D * U * 512 bytes) filled by
+// per-lane cp.async copies instead of in registers, so D * U rows per lane are
+// in flight (against U) and the row registers are free; the walk, the stores
+// and the patch pass are the same.
+template <typename T, int V, int U, bool IDX64, int D = 0>
+__device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_t b1, int lane,
+                                            unsigned char* ring = nullptr) {
+  static_assert(D == 0 || V * sizeof(T) == 16, "the ring holds 16-byte lane cells");
   using Ops = RowOps<T, V>;
   using IdxT = typename IdxOf<IDX64>::type;
   const int lgG = c.lg_group, lgR = 5 - lgG, G = 1 << lgG, R = 1 << lgR;
@@ -540,47 +600,107 @@ __device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_
       float acc[V];
       zero_vals<V>(acc);
 
-      for (int k = 0; k < ls; k += U) {
-        int p[U];
-        bool ok[U];
-        typename Ops::Raw rows[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          p[u] = e + u;
-          ok[u] = p[u] < e_end;
-        }
-        const bool inner = (e + U < kend) && (e + U <= e_end);
-        if (__all_sync(kFull, inner)) {
-          fetch_rows<T, V, U, IDX64, false>(c, vp, tcol, col_ok, p, ok, rows);
-#pragma unroll
-          for (int u = 0; u < U; ++u) Ops::add(acc, rows[u]);
-          e += U;
-        } else {
-          fetch_rows<T, V, U, IDX64, true>(c, vp, tcol, col_ok, p, ok, rows);
-#pragma unroll
+      if constexpr (D == 0) {
+        for (int k = 0; k < ls; k += U) {
+          int p[U];
+          bool ok[U];
+          typename Ops::Raw rows[U];
+  #pragma unroll
           for (int u = 0; u < U; ++u) {
-            Ops::add(acc, rows[u]);
-            const bool at_end = ok[u] && (e + 1 == kend);
-            if (__any_sync(kFull, at_end)) {
-              const unsigned rest = kb >= 31 ? 0u : (nz & (0xfffffffeu << kb));
-              const int nkb = rest ? (__ffs(rest) - 1) : 31;
-              int nend = __shfl_sync(kFull, ch.hi, nkb);
-              if (!rest) nend = 0x7fffffff;
-              if (at_end) {
-                if (col_ok) store_vals<V>(orow + (int64_t)kb * c.out_ld, acc, c.out_vec);
-                if (head_pending) {
-                  had_head = true;
-                  head_bag = kb;
-                  head_pending = false;
+            p[u] = e + u;
+            ok[u] = p[u] < e_end;
+          }
+          const bool inner = (e + U < kend) && (e + U <= e_end);
+          if (__all_sync(kFull, inner)) {
+            fetch_rows<T, V, U, IDX64, false>(c, vp, tcol, col_ok, p, ok, rows);
+  #pragma unroll
+            for (int u = 0; u < U; ++u) Ops::add(acc, rows[u]);
+            e += U;
+          } else {
+            fetch_rows<T, V, U, IDX64, true>(c, vp, tcol, col_ok, p, ok, rows);
+  #pragma unroll
+            for (int u = 0; u < U; ++u) {
+              Ops::add(acc, rows[u]);
+              const bool at_end = ok[u] && (e + 1 == kend);
+              if (__any_sync(kFull, at_end)) {
+                const unsigned rest = kb >= 31 ? 0u : (nz & (0xfffffffeu << kb));
+                const int nkb = rest ? (__ffs(rest) - 1) : 31;
+                int nend = __shfl_sync(kFull, ch.hi, nkb);
+                if (!rest) nend = 0x7fffffff;
+                if (at_end) {
+                  if (col_ok) store_vals<V>(orow + (int64_t)kb * c.out_ld, acc, c.out_vec);
+                  if (head_pending) {
+                    had_head = true;
+                    head_bag = kb;
+                    head_pending = false;
+                  }
+                  zero_vals<V>(acc);
+                  kb = nkb;
+                  kend = nend;
                 }
-                zero_vals<V>(acc);
-                kb = nkb;
-                kend = nend;
               }
+              e += ok[u] ? 1 : 0;
             }
-            e += ok[u] ? 1 : 0;
           }
         }
+      } else {
+        const unsigned cell = smem_addr(ring) + lane * 16;  // my 16-byte cell of ring slot 0, entry 0
+        const int nsteps = (ls + U - 1) / U;
+        IdxT idx[U];
+        load_indices<U, IDX64>(vp, s, e_end, col_ok, idx);
+#pragma unroll
+        for (int pm = 0; pm < D - 1; ++pm) {  // fill the pipeline
+          issue_rows<T, U, IDX64>(c, tcol, col_ok, idx, s + pm * U, e_end, cell + pm * U * 512);
+          cp_async_commit();
+          load_indices<U, IDX64>(vp, s + (pm + 1) * U, e_end, col_ok, idx);
+        }
+        int slot_in = D - 1, slot_out = 0;
+        for (int m = 0; m < nsteps; ++m) {
+          issue_rows<T, U, IDX64>(c, tcol, col_ok, idx, s + (m + D - 1) * U, e_end, cell + slot_in * U * 512);
+          cp_async_commit();
+          load_indices<U, IDX64>(vp, s + (m + D) * U, e_end, col_ok, idx);  // indices one macro-step ahead of their copies
+          cp_async_wait<D - 1>();
+          bool ok[U];
+          typename Ops::Raw rows[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            ok[u] = e + u < e_end;
+            rows[u] = lds16(cell + (slot_out * U + u) * 512);
+          }
+          const bool inner = (e + U < kend) && (e + U <= e_end);
+          if (__all_sync(kFull, inner)) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) Ops::add(acc, rows[u]);
+            e += U;
+          } else {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              Ops::add(acc, rows[u]);
+              const bool at_end = ok[u] && (e + 1 == kend);
+              if (__any_sync(kFull, at_end)) {
+                const unsigned rest = kb >= 31 ? 0u : (nz & (0xfffffffeu << kb));
+                const int nkb = rest ? (__ffs(rest) - 1) : 31;
+                int nend = __shfl_sync(kFull, ch.hi, nkb);
+                if (!rest) nend = 0x7fffffff;
+                if (at_end) {
+                  if (col_ok) store_vals<V>(orow + (int64_t)kb * c.out_ld, acc, c.out_vec);
+                  if (head_pending) {
+                    had_head = true;
+                    head_bag = kb;
+                    head_pending = false;
+                  }
+                  zero_vals<V>(acc);
+                  kb = nkb;
+                  kend = nend;
+                }
+              }
+              e += ok[u] ? 1 : 0;
+            }
+          }
+          slot_in = slot_in + 1 == D ? 0 : slot_in + 1;
+          slot_out = slot_out + 1 == D ? 0 : slot_out + 1;
+        }
+        cp_async_wait<0>();  // the ring is reused by the next chunk
       }
 
       // patch the bags cut by piece boundaries

@@ -34,7 +34,7 @@ def _device_index(device) -> int:
 
 
 class Schedule:
-    """One feature's schedule: kind ('auto' | 'group' | 'warp' | 'flat' | 'stream'), unroll, bags_per_tile.
+    """One feature's schedule: kind ('auto' | 'group' | 'warp' | 'flat' | 'stream' | 'pipe'), unroll, bags_per_tile.
 
     The counterpart of the reference's (ScheduleBase subclass, params NamedTuple)
     pair (code_emitter/schedule_base.py:54-87); see include/recflex_b200.h for

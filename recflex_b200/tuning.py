@@ -35,7 +35,7 @@ import torch
 
 from .rec_modules import FeatEmbed, Schedule
 
-KINDS = ("group", "warp", "flat", "stream")
+KINDS = ("group", "warp", "flat", "stream", "pipe")
 UNROLLS = (1, 2, 4, 8)
 
 
@@ -43,7 +43,7 @@ UNROLLS = (1, 2, 4, 8)
 class TuneConfig:
     """Search space and effort (reference: `TuneConfig`, tuner.py:38-46, and each schedule's GenParamCandidates)."""
 
-    occupancies: Sequence[int] = (3, 4, 5, 6, 8)
+    occupancies: Sequence[int] = (2, 3, 4, 5, 6, 8)
     kinds: Sequence[str] = KINDS
     unrolls: Sequence[int] = UNROLLS
     reps: int = 2                 # launches per (feature, occupancy) in the local stage
@@ -51,7 +51,8 @@ class TuneConfig:
     min_replicas: int = 16        # candidates are repeated until at least this many replicas fill the GPU
     cluster: bool = True          # tune one representative per cluster of look-alike features
     max_probe_bytes: int = 2 << 30  # cap of the local stage's output buffer
-    uniform_portfolio: Sequence[Tuple[str, int]] = (("stream", 2), ("stream", 4), ("stream", 8), ("warp", 4))
+    uniform_portfolio: Sequence[Tuple[str, int]] = (("stream", 2), ("stream", 4), ("stream", 8), ("warp", 4),
+                                                    ("pipe", 2), ("pipe", 4), ("pipe", 8))
     refine_top: int = 3           # local-stage candidates tried per cluster in the refinement pass (0 = off)
     refine_min_gain: float = 0.003  # a switch must make the fused kernel this much faster (relative) to be kept
 
@@ -151,6 +152,8 @@ class Tuner:
                     continue  # a slot walking hundreds of rows alone leaves the other slots idle
                 if kind in ("warp", "group") and u > 1 and st.max_len <= 1:
                     continue  # one-hot: a bag never has a second row to keep in flight
+                if kind == "pipe" and u == 1:
+                    continue  # the ring's shallowest variant is unroll 2
                 cands.append(Schedule(kind, u))
         return cands
 

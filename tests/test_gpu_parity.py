@@ -10,7 +10,7 @@ from tests.helpers import (TOL, all_schedules, check_against_oracle, device_tabl
 
 pytestmark = pytest.mark.gpu
 
-KINDS = ["group", "warp", "flat", "stream"]
+KINDS = ["group", "warp", "flat", "stream", "pipe"]
 UNROLLS = [1, 2, 4, 8]
 
 

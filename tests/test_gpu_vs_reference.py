@@ -60,7 +60,7 @@ def test_matches_reference_device_templates(ref, cfg_id, scale, batch, ref_kind)
     expect = reference_kernels_output(ref, ref_kind, tables_dev, dv, do, onehot_feats=onehot)
     assert not torch.isnan(expect).any()
     mod = FeatEmbed("cuda:0", embed_tables=tables_dev)
-    for kind in ("stream", "flat", "warp", "group"):
+    for kind in ("stream", "pipe", "flat", "warp", "group"):
         mod.set_schedules(all_schedules(kind, 4, len(tables)))
         out = mod(dv, do)
         mod.check_status()
@@ -72,7 +72,7 @@ def test_golden_fixtures_through_the_text_front_end(name):
     tables, raw, expect = load_case(name)
     model = FeatProcessEmbed(None, 0, embed_tables=device_tables(tables))
     tag = "f16" if tables[0].dtype == np.float16 else "f32"
-    for kind in ("stream", "flat", "warp", "group"):
+    for kind in ("stream", "pipe", "flat", "warp", "group"):
         model.embed_layer.set_schedules(all_schedules(kind, 2, len(tables)))
         out = model(raw)
         np.testing.assert_allclose(out.cpu().numpy(), expect, **TOL[tag])
