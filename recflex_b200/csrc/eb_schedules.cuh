@@ -509,26 +509,29 @@ __device__ __forceinline__ void load_indices(const typename IdxOf<IDX64>::type* 
 }
 
 // Issue the copies of one macro-step (U entries starting at `first`) into ring cells dst + u * 512.
+// Entries at or past `limit` carry index 0 (see load_indices), so every source address is inside the table;
+// they and out-of-range indices copy zero bytes (the cell is zero-filled).  Returns whether a bad index was met.
 template <typename T, int U, bool IDX64>
-__device__ __forceinline__ void issue_rows(const TileCtx& c, const char* tcol, bool col_ok,
+__device__ __forceinline__ bool issue_rows(const TileCtx& c, const char* tcol, bool col_ok,
                                            const typename IdxOf<IDX64>::type (&idx)[U], int first, int limit,
                                            unsigned dst) {
   const unsigned rows32 = c.rows > 0x80000000ll ? 0x80000000u : (unsigned)c.rows;
+  bool bad = false;
 #pragma unroll
   for (int u = 0; u < U; ++u) {
     const bool ok = col_ok && first + u < limit;
-    bool valid;
-    const char* src;
     if constexpr (IDX64) {
-      valid = (uint64_t)idx[u] < (uint64_t)c.rows;
-      src = tcol + (valid ? idx[u] : 0) * (int64_t)c.row_bytes;
+      const bool valid = (uint64_t)idx[u] < (uint64_t)c.rows;
+      bad |= ok && !valid;
+      cp_async16(dst + u * 512, tcol + (valid ? idx[u] : 0) * (int64_t)c.row_bytes, ok && valid ? 16u : 0u);
     } else {
-      valid = (unsigned)idx[u] < rows32;
-      src = tcol + (uint64_t)(valid ? (unsigned)idx[u] : 0u) * (unsigned)c.row_bytes;
+      const unsigned i = (unsigned)idx[u];
+      const bool valid = i < rows32;
+      bad |= ok && !valid;
+      cp_async16(dst + u * 512, tcol + (uint64_t)min(i, rows32 - 1u) * (unsigned)c.row_bytes, ok && valid ? 16u : 0u);
     }
-    if (ok && !valid) flag(c.status, kStatusBadIndex);
-    cp_async16(dst + u * 512, ok && valid ? src : c.table, ok && valid ? 16u : 0u);
   }
+  return bad;
 }
 
 // ---------------------------------------------------------------------------
@@ -647,16 +650,18 @@ __device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_
         const unsigned cell = smem_addr(ring) + lane * 16;  // my 16-byte cell of ring slot 0, entry 0
         const int nsteps = (ls + U - 1) / U;
         IdxT idx[U];
+        bool bad = false;
         load_indices<U, IDX64>(vp, s, e_end, col_ok, idx);
 #pragma unroll
         for (int pm = 0; pm < D - 1; ++pm) {  // fill the pipeline
-          issue_rows<T, U, IDX64>(c, tcol, col_ok, idx, s + pm * U, e_end, cell + pm * U * 512);
+          bad |= issue_rows<T, U, IDX64>(c, tcol, col_ok, idx, s + pm * U, e_end, cell + pm * U * 512);
           cp_async_commit();
           load_indices<U, IDX64>(vp, s + (pm + 1) * U, e_end, col_ok, idx);
         }
-        int slot_in = D - 1, slot_out = 0;
+        unsigned cell_in = cell + (D - 1) * U * 512, cell_out = cell;  // ring cursors
+        const unsigned cell_end = cell + D * U * 512;
         for (int m = 0; m < nsteps; ++m) {
-          issue_rows<T, U, IDX64>(c, tcol, col_ok, idx, s + (m + D - 1) * U, e_end, cell + slot_in * U * 512);
+          bad |= issue_rows<T, U, IDX64>(c, tcol, col_ok, idx, s + (m + D - 1) * U, e_end, cell_in);
           cp_async_commit();
           load_indices<U, IDX64>(vp, s + (m + D) * U, e_end, col_ok, idx);  // indices one macro-step ahead of their copies
           cp_async_wait<D - 1>();
@@ -665,7 +670,7 @@ __device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_
 #pragma unroll
           for (int u = 0; u < U; ++u) {
             ok[u] = e + u < e_end;
-            rows[u] = lds16(cell + (slot_out * U + u) * 512);
+            rows[u] = lds16(cell_out + u * 512);
           }
           const bool inner = (e + U < kend) && (e + U <= e_end);
           if (__all_sync(kFull, inner)) {
@@ -697,10 +702,13 @@ __device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_
               e += ok[u] ? 1 : 0;
             }
           }
-          slot_in = slot_in + 1 == D ? 0 : slot_in + 1;
-          slot_out = slot_out + 1 == D ? 0 : slot_out + 1;
+          cell_in += U * 512;
+          if (cell_in == cell_end) cell_in = cell;
+          cell_out += U * 512;
+          if (cell_out == cell_end) cell_out = cell;
         }
         cp_async_wait<0>();  // the ring is reused by the next chunk
+        if (bad) flag(c.status, kStatusBadIndex);
       }
 
       // patch the bags cut by piece boundaries
