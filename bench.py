@@ -281,6 +281,16 @@ def run_ours(args):
     out = torch.empty((B, cfg.output_units), dtype=torch.float32, device=dev)
     host_out = torch.empty((B, cfg.output_units), dtype=torch.float32).pin_memory()
     nb = args.batches
+    if args.tune:
+        from recflex_b200.tuning import TuneConfig, Tuner
+
+        tb = [([torch.from_numpy(v).to(dev) for v in first[0]], [torch.from_numpy(o).to(dev) for o in first[1]])]
+        res = Tuner(mod, tb, TuneConfig()).tune()
+        sched_note = f"tuned before timing (occupancy {res.occupancy})"
+        if args.schedules:
+            res.save(args.schedules, workload=cfg.name)
+        del tb
+        _, occupancy = mod.get_schedules()
 
     for i in range(max(3, args.warmup)):
         mod.forward_packed(dev_v[i % nb], dev_o[i % nb], out=out)
@@ -305,15 +315,32 @@ def run_ours(args):
     mod.kernel_timing(False)
 
     # ---- timed region B: host buffers in, host result out ----
+    # Two handles over the same tables alternate on two streams, so that step k + 1's upload overlaps step k's
+    # download (PCIe is full duplex); each call is still upload -> bind + fused kernel -> download of its result.
     t_e2e = None
     if not args.no_e2e:
-        for i in range(2):
-            mod.forward_host(host_v[i % nb], host_o[i % nb], out=host_out)
+        mod_b = FeatEmbed(dev, embed_tables=tables)
+        scheds, occ_b = mod.get_schedules()
+        mod_b.set_schedules(scheds, occupancy=occ_b)
+        lanes = [(mod, torch.cuda.Stream(device=dev), host_out),
+                 (mod_b, torch.cuda.Stream(device=dev), torch.empty_like(host_out).pin_memory())]
+
+        def e2e_steps(n):
+            main = torch.cuda.current_stream(dev)
+            for _, st, _ in lanes:
+                st.wait_stream(main)
+            for i in range(n):
+                m, st, ho = lanes[i % 2]
+                with torch.cuda.stream(st):
+                    m.forward_host(host_v[i % nb], host_o[i % nb], out=ho)
+            for _, st, _ in lanes:
+                main.wait_stream(st)
+
+        e2e_steps(2)
         barrier()
         ev2, ev3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev2.record()
-        for i in range(K):
-            mod.forward_host(host_v[i % nb], host_o[i % nb], out=host_out)
+        e2e_steps(K)
         ev3.record()
         barrier()
         t_e2e = ev2.elapsed_time(ev3) * 1e-3
@@ -359,7 +386,7 @@ def run_ours(args):
             },
             "e2e": {"value": world * K * B / t_e2e if t_e2e else None, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": t_e2e / K * 1e3 if t_e2e else None},
-            "gpu_launches": 2 * K,
+            "gpu_launches": 2 * K + (2 * K if t_e2e else 0),
             "clocks": sampler.summary(),
         }
         if world == 1 and not args.no_cpu_baseline:

@@ -1,6 +1,6 @@
 """Generates the golden fixtures of tests/golden/ from the RecFlex reference itself.
 
-Run in a container that has the reference checkout (default /root/reference) and
+Run in a container that has the reference checkout (path as argument or in $RECFLEX_REF) and
 after `bash oracle/build_ref.sh`:
 
     python tests/golden/make_golden.py [/path/to/RecFlex]
@@ -31,7 +31,7 @@ import torch.nn.functional as F
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("RECFLEX_REF", "/root/reference")
 sys.dont_write_bytecode = True
 sys.path.insert(0, REF)
 sys.path.insert(0, os.path.join(REF, "examples"))
