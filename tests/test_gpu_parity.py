@@ -227,3 +227,49 @@ def test_cuda_graph_capture_and_replay(cfg1):
         graph.replay()
         torch.cuda.synchronize()
         check_against_oracle(out, tables, v, o, "f32")
+
+
+@pytest.mark.parametrize("kind", KINDS)
+def test_int64_every_kind(kind):
+    cfg, tables, values, offsets = small_model(3, 2e-4, 300)
+    mod = FeatEmbed("cuda:0", embed_tables=device_tables(tables))
+    mod.set_schedules(all_schedules(kind, 8, len(tables)))  # 64-bit indices always run at unroll 4
+    out = mod(to_device(values, dtype=np.int64), to_device(offsets, dtype=np.int64))
+    mod.check_status()
+    check_against_oracle(out, tables, values, offsets, "f16")
+
+
+def test_random_models_every_kind():
+    """Fuzz: random dims (also not multiples of 4), dtypes, table sizes, length patterns, batch sizes, mixed kinds."""
+    rng = np.random.default_rng(2024)
+    for trial in range(24):
+        F = int(rng.integers(1, 9))
+        batch = int(rng.choice([1, 2, 17, 32, 33, 64, 100, 257]))
+        tables, values, offsets, scheds = [], [], [], []
+        for f in range(F):
+            dim = int(rng.choice([1, 2, 3, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256, 320, 512]))
+            rows = int(rng.integers(1, 2000))
+            dt = np.float16 if rng.random() < 0.5 else np.float32
+            tables.append((rng.standard_normal((rows, dim)) * 0.1).astype(dt))
+            mode = int(rng.integers(0, 5))
+            if mode == 0:
+                lens = np.ones(batch, dtype=np.int64)
+            elif mode == 1:
+                lens = rng.integers(0, 3, batch)
+            elif mode == 2:
+                lens = rng.integers(0, 40, batch)
+            elif mode == 3:
+                lens = (rng.pareto(0.7, batch)).astype(np.int64).clip(0, 600)
+            else:
+                lens = np.zeros(batch, dtype=np.int64)
+            o = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+            offsets.append(o)
+            values.append(rng.integers(0, rows, o[-1]).astype(np.int32))
+            scheds.append(Schedule(str(rng.choice(KINDS)), int(rng.choice([1, 2, 4, 8]))))
+        mod = FeatEmbed("cuda:0", embed_tables=device_tables(tables))
+        mod.set_schedules(scheds, occupancy=int(rng.integers(1, 9)))
+        out = mod(to_device(values), to_device(offsets))
+        mod.check_status()
+        expect = oracle.pool(tables, values, offsets, acc64=True)
+        np.testing.assert_allclose(out.cpu().numpy(), expect, rtol=2e-3, atol=2e-5,
+                                   err_msg=f"trial {trial}: {[(t.shape, t.dtype) for t in tables]} {scheds}")
