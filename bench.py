@@ -60,6 +60,10 @@ def parse_args():
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--chunks", type=int, default=4, help="batch chunks of the sharded path (exchange/pooling overlap)")
     p.add_argument("--tune", action="store_true", help="run the two-stage tuner on the first batch before timing (untimed)")
+    p.add_argument("--emulate-world", type=int, default=0,
+                   help="sharded workloads on ONE GPU: build only rank --emulate-rank's shard of a sharding over this "
+                        "many ranks and time its pooling alone (no exchange); for profiling a shard")
+    p.add_argument("--emulate-rank", type=int, default=0)
     p.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
                    help="sharded path: fused peer-memory stores, or pool + NCCL all-to-all + placement")
     return p.parse_args()
@@ -398,6 +402,53 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_shard_emulation(args):
+    """One rank's shard of cfg4 on a single GPU: pooling only, for profiling (not a benchmark line of the job)."""
+    import torch
+
+    from recflex_b200 import synth
+    from recflex_b200.rec_modules import FeatEmbed
+    from recflex_b200.sharding import plan_shards
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    cfg = synth.make_config(WORKLOADS[args.workload], row_scale=args.row_scale, batch=args.batch or None)
+    W, R, B = args.emulate_world, args.emulate_rank, cfg.batch
+    owner = plan_shards([fs.table_bytes for fs in cfg.features], synth.expected_traffic(cfg), W,
+                        int(torch.cuda.mem_get_info(dev)[1] * 0.88))
+    local = [f for f, r in enumerate(owner) if r == R]
+    mod = FeatEmbed(dev, embed_tables=synth.make_tables_device(cfg, dev, features=local))
+    mod.set_schedules(None, occupancy=args.occupancy or 6)
+    batches, alg = [], []
+    for i in range(args.batches):
+        vs, os_, nbytes = [], [], 0
+        for f in local:
+            v, o = synth.gen_feature_batch(cfg.features[f], B, seed=i)
+            nbytes += int(o[-1]) * cfg.features[f].row_bytes + int(o[-1]) * 4 + len(o) * 4
+            vs.append(torch.from_numpy(v.astype(np.int32)).to(dev))
+            os_.append(torch.from_numpy(o.astype(np.int32)).to(dev))
+        batches.append((vs, os_))
+        alg.append(nbytes)
+    if args.tune:
+        from recflex_b200.tuning import TuneConfig, Tuner
+
+        Tuner(mod, [batches[0]], TuneConfig(occupancies=(3, 4, 5, 6, 8), reps=1, global_reps=2)).tune()
+    out = torch.empty((B, mod.output_units), dtype=torch.float32, device=dev)
+    for i in range(max(3, args.warmup)):
+        mod(*batches[i % len(batches)], out=out)
+    mod.kernel_timing(True)
+    for i in range(args.steps):
+        mod(*batches[i % len(batches)], out=out)
+    kt = mod.kernel_times()
+    k_ms = statistics.mean(kt)
+    scheds, occ = mod.get_schedules()
+    print(json.dumps({"emulated_rank": R, "of": W, "workload": cfg.name, "local_features": len(local),
+                      "table_gb": round(sum(cfg.features[f].table_bytes for f in local) / 1e9, 1),
+                      "kernel_ms": k_ms, "algorithmic_bytes_per_launch": statistics.mean(alg),
+                      "algorithmic_gbs": statistics.mean(alg) / (k_ms * 1e-3) / 1e9, "occupancy": occ,
+                      "note": "pooling of one shard only; no exchange"}), flush=True)
+
+
 def run_sharded(args):
     """cfg4: tables sharded table-wise over the ranks, pooled outputs exchanged with an all-to-all."""
     import torch
@@ -561,6 +612,8 @@ def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "cfg4" and args.emulate_world:
+        run_shard_emulation(args)
     elif args.workload == "cfg4":
         run_sharded(args)
     else:
