@@ -281,6 +281,18 @@ int eb_place_columns(const float* src, float* dst, int64_t rows, int64_t dst_ld,
                      const void* segments, int device, void* stream);
 
 /*
+ * Device-side ingestion of a lengths-based jagged batch: `lengths` is a DEVICE
+ * [num_features, batch] matrix of bag lengths (values and lengths share one
+ * integer dtype); writes the DEVICE [num_features, batch + 1] offsets matrix
+ * eb_forward_packed expects (row f = exclusive prefix sum of feature f's
+ * lengths, last entry = nnz_f).  Replaces the offsets part of the host
+ * preprocess (examples/csrc/warp_per_sample_preprocess.cu:14-33: the running
+ * segment_offsets) for inputs that arrive as lengths.
+ */
+int eb_offsets_from_lengths(const void* lengths, void* offsets, int32_t num_features, int64_t batch,
+                            int index_dtype, int device, void* stream);
+
+/*
  * Host-side parser of the reference's text input: `text` holds `batch` lines
  * separated by '\n' (one bag per line, indices separated by any non-digit
  * character, an empty line is an empty bag).  Writes the indices to values_out

@@ -82,6 +82,7 @@ PROTOTYPES = {
     "eb_peer_free": (C.c_int, [C.c_int, C.c_void_p]),
     "eb_place_columns": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_void_p, C.c_int,
                                    C.c_void_p]),
+    "eb_offsets_from_lengths": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int, C.c_int, C.c_void_p]),
     "eb_parse_bags": (C.c_int, [C.c_char_p, C.c_size_t, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p,
                                 C.POINTER(C.c_int64)]),
     "eb_forward_packed_noalloc": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_int64), C.POINTER(C.c_int32),

@@ -219,4 +219,31 @@ __global__ void __launch_bounds__(256) eb_place_kernel(const float* __restrict__
   }
 }
 
+// ---------------------------------------------------------------------------
+// lengths -> offsets: one CTA per feature scans that feature's batch of bag
+// lengths into batch + 1 exclusive offsets (offsets[f][0] = 0, offsets[f][B] =
+// nnz_f).  Negative lengths count as 0.
+// ---------------------------------------------------------------------------
+template <typename IdxT>
+__global__ void __launch_bounds__(kBindThreads) eb_lengths_kernel(const IdxT* __restrict__ lengths,
+                                                                  IdxT* __restrict__ offsets, long long batch) {
+  __shared__ long long s_warp[32];
+  const IdxT* len = lengths + (long long)blockIdx.x * batch;
+  IdxT* off = offsets + (long long)blockIdx.x * (batch + 1);
+  long long carry = 0;
+  for (long long base = 0; base < batch; base += kBindThreads) {
+    const long long i = base + threadIdx.x;
+    long long v = 0;
+    if (i < batch) {
+      v = (long long)len[i];
+      if (v < 0) v = 0;
+    }
+    long long total;
+    const long long excl = block_excl_scan(v, s_warp, total) + carry;
+    if (i < batch) off[i] = (IdxT)excl;
+    carry += total;
+  }
+  if (threadIdx.x == 0) off[batch] = (IdxT)carry;
+}
+
 }  // namespace ebk

@@ -610,6 +610,19 @@ int eb_place_columns(const float* src, float* dst, int64_t rows, int64_t dst_ld,
   return EB_OK;
 }
 
+int eb_offsets_from_lengths(const void* lengths, void* offsets, int32_t num_features, int64_t batch, int index_dtype,
+                            int device, void* stream) {
+  if (num_features < 0 || batch < 0) return fail(EB_ERR_INVALID_ARG, "negative size");
+  if (index_dtype != EB_I32 && index_dtype != EB_I64) return fail(EB_ERR_INVALID_ARG, "bad index_dtype %d", index_dtype);
+  if (num_features == 0) return EB_OK;
+  if (!offsets || (batch > 0 && !lengths)) return fail(EB_ERR_INVALID_ARG, "null pointer");
+  if (num_features > 65535 * 32768) return fail(EB_ERR_TOO_LARGE, "too many features");
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(EB_ERR_CUDA, "cannot select device %d", device);
+  EB_CUDA(launch_lengths(lengths, offsets, num_features, batch, index_dtype == EB_I64, static_cast<cudaStream_t>(stream)));
+  return EB_OK;
+}
+
 int eb_parse_bags(const char* text, size_t text_len, int64_t batch, int32_t* values_out, int64_t values_cap,
                   int32_t* offsets_out, int64_t* nnz_out) {
   if ((!text && text_len) || batch < 0 || !offsets_out || !nnz_out || (values_cap > 0 && !values_out))

@@ -78,4 +78,16 @@ cudaError_t launch_place(const float* src, float* dst, int64_t rows, int64_t dst
   return cudaGetLastError();
 }
 
+cudaError_t launch_lengths(const void* lengths, void* offsets, int num_features, int64_t batch, int idx64,
+                           cudaStream_t st) {
+  if (num_features == 0) return cudaSuccess;
+  if (idx64)
+    eb_lengths_kernel<long long><<<num_features, kBindThreads, 0, st>>>(static_cast<const long long*>(lengths),
+                                                                        static_cast<long long*>(offsets), batch);
+  else
+    eb_lengths_kernel<int><<<num_features, kBindThreads, 0, st>>>(static_cast<const int*>(lengths),
+                                                                  static_cast<int*>(offsets), batch);
+  return cudaGetLastError();
+}
+
 }  // namespace ebk

@@ -25,6 +25,9 @@ cudaError_t fused_ctas_per_sm(int occupancy, size_t smem_bytes, int* per_sm);
 cudaError_t launch_place(const float* src, float* dst, int64_t rows, int64_t dst_ld, int num_segments,
                          const void* segments, int vec_ok, cudaStream_t st);
 
+cudaError_t launch_lengths(const void* lengths, void* offsets, int num_features, int64_t batch, int idx64,
+                           cudaStream_t st);
+
 // Sets the calling thread's eb_last_error() message (defined beside it).
 void set_last_error(const char* msg);
 

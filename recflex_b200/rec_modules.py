@@ -265,6 +265,20 @@ class FeatEmbed(nn.Module):
                                                C.c_void_p(self._ws_ptr), self._ws_bytes, self._stream()))
         return out
 
+    def offsets_from_lengths(self, lengths: torch.Tensor) -> torch.Tensor:
+        """Device tensor `[num_features, batch]` of bag lengths -> `[num_features, batch + 1]` offsets for
+        `forward_packed` (computed on the device, no host pass)."""
+        if lengths.dim() != 2 or lengths.shape[0] != self.num_features or not lengths.is_contiguous():
+            raise ValueError("lengths must be a contiguous [num_features, batch] tensor")
+        if lengths.device != self.device:
+            raise ValueError(f"lengths must live on {self.device}")
+        idt = self._index_dtype(lengths)
+        offsets = torch.empty((self.num_features, lengths.shape[1] + 1), dtype=lengths.dtype, device=self.device)
+        _lib.check(self._lib.eb_offsets_from_lengths(C.c_void_p(lengths.data_ptr()), C.c_void_p(offsets.data_ptr()),
+                                                     self.num_features, lengths.shape[1], idt, self.device.index,
+                                                     self._stream()))
+        return offsets
+
     def forward_host(self, values: torch.Tensor, offsets: torch.Tensor, out: Optional[torch.Tensor] = None):
         """End-to-end call on HOST tensors (pinned for full copy speed): uploads the packed batch,
         runs the forward and downloads the `[batch, output_units]` result into `out` (a host

@@ -273,3 +273,20 @@ def test_random_models_every_kind():
         expect = oracle.pool(tables, values, offsets, acc64=True)
         np.testing.assert_allclose(out.cpu().numpy(), expect, rtol=2e-3, atol=2e-5,
                                    err_msg=f"trial {trial}: {[(t.shape, t.dtype) for t in tables]} {scheds}")
+
+
+@pytest.mark.parametrize("dtype", [np.int32, np.int64])
+def test_offsets_from_lengths_on_device(cfg1, dtype):
+    cfg, tables, values, offsets, mod = cfg1
+    for batch in (1, 255, 1024, 5000):
+        rng = np.random.default_rng(batch)
+        lens = rng.integers(0, 9, (len(tables), batch)).astype(dtype)
+        got = mod.offsets_from_lengths(torch.from_numpy(lens).cuda()).cpu().numpy()
+        expect = np.concatenate([np.zeros((len(tables), 1), dtype=dtype), np.cumsum(lens, axis=1, dtype=dtype)], axis=1)
+        assert got.dtype == dtype and np.array_equal(got, expect)
+    # lengths -> offsets -> packed forward equals the list forward
+    mod.set_schedules(all_schedules("stream", 4, len(tables)), occupancy=4)
+    pv, po = synth.pack_batch(values, offsets)
+    lens = torch.from_numpy(np.diff(po, axis=1).astype(dtype)).cuda()
+    out = mod.forward_packed(torch.from_numpy(pv.astype(dtype)).cuda(), mod.offsets_from_lengths(lens))
+    check_against_oracle(out, tables, values, offsets, "f32")
