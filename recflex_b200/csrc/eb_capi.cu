@@ -315,7 +315,9 @@ int eb_set_schedules(eb_handle* h, const eb_schedule* per_feature, int occupancy
       const int rc = check_schedule(per_feature[f], f);
       if (rc != EB_OK) return rc;
     }
-    int cells = 0;  // deepest ring any pipelined feature needs: unroll 2 -> 2 x 4, 4 -> 4 x 3, 8 -> 8 x 2
+    // deepest ring any pipelined feature needs: unroll 2 -> 2 x 4 cells, 4 -> 4 x 3, 8 -> 8 x 2; never fewer than
+    // 12, because batches with 64-bit indices always run the unroll-4 / 3-stage variant whatever was requested
+    int cells = 0;
     for (int f = 0; f < h->num_features; ++f) {
       h->sched[f] = resolve(per_feature[f]);
       // the ring holds 16-byte lane cells: element-wise fallback rows keep the register walk
@@ -323,7 +325,7 @@ int eb_set_schedules(eb_handle* h, const eb_schedule* per_feature, int occupancy
       apply_schedule(h->feats[f], h->sched[f]);
       if (h->sched[f].kind == EB_SCHED_PIPE) {
         const int u = h->sched[f].unroll;
-        const int need = u <= 2 ? 8 : (u == 4 ? 12 : 16);
+        const int need = u == 8 ? 16 : 12;
         cells = need > cells ? need : cells;
       }
     }

@@ -220,16 +220,45 @@ struct IdxOf<true> { using type = long long; };
 
 // Fetch U rows: indices vp[p[u]] -> rows.  With 32-bit indices the bounds check
 // is one unsigned compare and the row address one 32x32+64 multiply-add.
-// CHECK = false skips the per-entry `ok` predicate (every entry is in range).
+// CHECK = false means every entry is in range (`ok` is not read).
+// When every lane's entries are in range and every index is valid (one warp
+// vote), the row loads are issued unconditionally: no predicates and no
+// zero-initialised buffers on the path that carries almost all the traffic.
+// Must be called by all 32 lanes.
 template <typename T, int V, int U, bool IDX64, bool CHECK>
 __device__ __forceinline__ void fetch_rows(const TileCtx& c, const typename IdxOf<IDX64>::type* vp,
                                            const char* tcol, bool col_ok, const int (&p)[U], const bool (&ok)[U],
                                            typename RowOps<T, V>::Raw (&rows)[U]) {
   using Ops = RowOps<T, V>;
   typename IdxOf<IDX64>::type idx[U];
+  bool all_ok = true;
 #pragma unroll
-  for (int u = 0; u < U; ++u) idx[u] = (col_ok && (!CHECK || ok[u])) ? __ldg(vp + p[u]) : 0;
+  for (int u = 0; u < U; ++u) {
+    const bool want = col_ok && (!CHECK || ok[u]);
+    idx[u] = want ? __ldg(vp + p[u]) : 0;
+    if (CHECK) all_ok = all_ok && (ok[u] || !col_ok);
+  }
   const unsigned rows32 = c.rows > 0x80000000ll ? 0x80000000u : (unsigned)c.rows;
+  bool valid = true;
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    if constexpr (IDX64) valid = valid && (uint64_t)idx[u] < (uint64_t)c.rows;
+    else valid = valid && (unsigned)idx[u] < rows32;
+  }
+  if (__all_sync(kFull, all_ok && valid)) {
+    // lanes whose columns lie past the row's end (col_ok false) load nothing; all others load unconditionally
+    if (col_ok) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if constexpr (IDX64) rows[u] = Ops::load(tcol + idx[u] * (int64_t)c.row_bytes);
+        else rows[u] = Ops::load(tcol + (uint64_t)(unsigned)idx[u] * (unsigned)c.row_bytes);
+      }
+    } else {
+#pragma unroll
+      for (int u = 0; u < U; ++u) rows[u] = Ops::zero();
+    }
+    return;
+  }
 #pragma unroll
   for (int u = 0; u < U; ++u) {
     rows[u] = Ops::zero();

@@ -290,3 +290,42 @@ def test_offsets_from_lengths_on_device(cfg1, dtype):
     lens = torch.from_numpy(np.diff(po, axis=1).astype(dtype)).cuda()
     out = mod.forward_packed(torch.from_numpy(pv.astype(dtype)).cuda(), mod.offsets_from_lengths(lens))
     check_against_oracle(out, tables, values, offsets, "f32")
+
+
+@pytest.mark.parametrize("kind", ["stream", "pipe", "warp", "flat"])
+@pytest.mark.parametrize("idt", [np.int32, np.int64])
+def test_long_bags(kind, idt):
+    """Bags of more than a thousand entries for every dim class (1 to 32 row slots per warp, and rows wider than a
+    warp), both table dtypes, 32- and 64-bit indices at every unroll (with 64-bit indices the pipelined schedule runs
+    its 12-cell variant whatever unroll was requested: its ring must be sized for that), an empty bag in between,
+    a bad index."""
+    rng = np.random.default_rng(77)
+    dims = [4, 8, 16, 32, 64, 128, 256, 8, 16, 32, 64, 128, 256, 512]
+    dts = [np.float32] * 7 + [np.float16] * 7
+    batch = 37
+    tables, values, offsets = [], [], []
+    for d, dt in zip(dims, dts):
+        rows = 300
+        tables.append((rng.standard_normal((rows, d)) * 0.05).astype(dt))
+        lens = rng.integers(1100, 1400, batch)
+        lens[5] = 0
+        o = np.concatenate([[0], np.cumsum(lens)]).astype(idt)
+        offsets.append(o)
+        values.append(rng.integers(0, rows, o[-1]).astype(idt))
+    mod = FeatEmbed("cuda:0", embed_tables=device_tables(tables))
+    for unroll, occ in ((4, 8), (2, 4), (8, 3)):
+        mod.set_schedules(all_schedules(kind, unroll, len(dims)), occupancy=occ)
+        out = mod(to_device(values), to_device(offsets))
+        mod.check_status()
+        expect = oracle.pool(tables, values, offsets, acc64=True)
+        np.testing.assert_allclose(out.cpu().numpy(), expect, rtol=2e-3, atol=2e-5)
+    bad = [v.copy() for v in values]
+    bad[2][1500] = 10 ** 6
+    out = mod(to_device(bad), to_device(offsets))
+    from recflex_b200._lib import EbError
+
+    with pytest.raises(EbError):
+        mod.check_status()
+    good = [v.copy() for v in values]
+    expect = oracle.pool(tables, bad, offsets, acc64=True, strict=False)  # the oracle skips the bad entry too
+    np.testing.assert_allclose(out.cpu().numpy(), expect, rtol=2e-3, atol=2e-5)
