@@ -52,9 +52,14 @@ extern "C" {
  *                   (warp_per_sample_kernel.cuh:10-82) and the one-hot row copy
  *                   onehot::GatherSegments (onehot_kernel.cuh:14-87).
  *   EB_SCHED_WARP   a whole warp owns one bag; its 32/(row_bytes/16) row slots
- *                   split the bag and are combined with warp shuffles.
- *                   Replaces obms::SparseSegmentReduce
- *                   (one_block_multi_sample_kernel.cuh:16-108).
+ *                   split the bag and are combined with warp shuffles.  For
+ *                   long, evenly sized bags.  These features are pooled by a
+ *                   separate lean kernel (one CTA per 8 bags, 8 CTAs per SM, two
+ *                   or four rows per lane in flight: unroll <= 2 -> 2, else 4)
+ *                   launched right before the fused kernel.  Replaces
+ *                   obms::SparseSegmentReduce
+ *                   (one_block_multi_sample_kernel.cuh:16-108) and, for long
+ *                   bags, ws::SparseSegmentReduce.
  *   EB_SCHED_FLAT   a warp streams the flattened index list of a run of bags,
  *                   dealing consecutive entries round-robin to its row slots,
  *                   keeps `unroll` rows per lane in flight regardless of bag

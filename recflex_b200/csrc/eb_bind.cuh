@@ -128,23 +128,38 @@ __global__ void __launch_bounds__(kBindThreads) eb_bind_kernel(LaunchArgs a, int
   }
   __syncthreads();
 
-  // pass 4: exclusive prefix sum of tile counts in that order
+  // pass 4: exclusive prefix sums of tile counts in that order, one per kernel: features on the warp-per-bag
+  // schedule (kind 2, vector path) are pooled by eb_warp_kernel, all others by eb_fused_kernel
+  int32_t* warp_prefix = reinterpret_cast<int32_t*>(a.ws + L.cta_prefix);
   carry = 0;
+  long long carry_w = 0;
   for (int base = 0; base < F; base += kBindThreads) {
     const int k = base + tid;
-    const long long t = k < F ? tiles_of(B, bpt[order[k]]) : 0;
+    long long t = 0, tw = 0;
+    if (k < F) {
+      const int f = order[k];
+      const bool lean = a.feats[f].kind == 2 && a.feats[f].vec != 0;
+      t = lean ? 0 : tiles_of(B, bpt[f]);
+      tw = lean ? (B + kWarpsPerCta - 1) / kWarpsPerCta : 0;  // eb_warp_kernel: one CTA per 8 bags
+    }
     long long total;
     const long long excl = block_excl_scan(t, s_warp, total) + carry;
     carry += total;
-    if (k < F) tile_prefix[k] = (int32_t)excl;
+    const long long excl_w = block_excl_scan(tw, s_warp, total) + carry_w;
+    carry_w += total;
+    if (k < F) {
+      tile_prefix[k] = (int32_t)excl;
+      warp_prefix[k] = (int32_t)excl_w;
+    }
   }
   status = __syncthreads_or((int)status);
   if (tid == 0) {
     tile_prefix[F] = (int32_t)carry;
+    warp_prefix[F] = (int32_t)carry_w;
     hdr->ticket = 0;
     hdr->total_tiles = (uint32_t)carry;
     hdr->cta_ticket = 0;
-    hdr->cta_tiles = 0;
+    hdr->cta_tiles = (uint32_t)carry_w;
     hdr->status = status;
   }
   if (tid < kMaxPeers) hdr->peer_out[tid] = a.peer_out[tid];

@@ -84,6 +84,7 @@ struct eb_handle {
   bool ev_used[kRing] = {};
   int ring_pos = 0;
   // optional event pairs around the fused-kernel launches
+  int warp_features = 0;   // features pooled by eb_warp_kernel (warp-per-bag schedule, vector path)
   size_t smem_bytes = 0;   // dynamic shared memory of the fused kernel (the pipelined schedule's rings)
   bool time_kernels = false;
   std::vector<cudaEvent_t> t0, t1;
@@ -171,6 +172,7 @@ int run(eb_handle* h, const LaunchArgs& a, bool timing, cudaStream_t st) {
   EB_CUDA(launch_bind(a, timing, st));
   const bool rec = h->time_kernels && h->t_count < kTimeRing;
   if (rec) EB_CUDA(cudaEventRecord(h->t0[h->t_count], st));
+  if (h->warp_features) EB_CUDA(launch_warp(a, timing, h->warp_features, st));
   EB_CUDA(launch_fused(a, h->occupancy, timing, h->sm_count * h->occupancy, h->smem_bytes, st));
   if (rec) {
     EB_CUDA(cudaEventRecord(h->t1[h->t_count], st));
@@ -330,6 +332,9 @@ int eb_set_schedules(eb_handle* h, const eb_schedule* per_feature, int occupancy
       }
     }
     h->smem_bytes = (size_t)cells * kPipeCellBytes * kWarpsPerCta;
+    h->warp_features = 0;
+    for (int f = 0; f < h->num_features; ++f)
+      h->warp_features += (h->feats[f].kind == EB_SCHED_WARP && h->feats[f].vec) ? 1 : 0;
     DeviceGuard guard(h->device);
     const int rc = upload_feats(h);
     if (rc != EB_OK) return rc;

@@ -1,3 +1,4 @@
+// (Features on the warp-per-bag schedule get no tiles here: eb_warp_kernel, eb_warp.cuh, pools them.)
 // eb_fused_kernel: persistent CTAs; every warp draws tile tickets, finds the
 // ticket's feature by binary search in the prefix sum that eb_bind_kernel
 // (eb_bind.cuh) left in the workspace and runs that feature's schedule.
@@ -56,8 +57,6 @@ namespace ebk {
     else tile_warp<float, 1, 4, true>(ctx, b0, b1, lane);          \
   } else if (fs.kind == 1) {                                       \
     EB_DISPATCH_DTYPE_U4(tile_group, true)                         \
-  } else if (fs.kind == 2) {                                       \
-    EB_DISPATCH_DTYPE_U4(tile_warp, true)                          \
   } else if (fs.kind == 3) {                                       \
     EB_DISPATCH_DTYPE_U4(tile_flat, true)                          \
   } else if (fs.kind == 4) {                                       \
@@ -73,8 +72,6 @@ namespace ebk {
     else tile_warp<float, 1, 4, I64>(ctx, b0, b1, lane);           \
   } else if (fs.kind == 1) {                                       \
     EB_DISPATCH_DTYPE(tile_group, I64)                             \
-  } else if (fs.kind == 2) {                                       \
-    EB_DISPATCH_DTYPE(tile_warp, I64)                              \
   } else if (fs.kind == 3) {                                       \
     EB_DISPATCH_DTYPE(tile_flat, I64)                              \
   } else if (fs.kind == 4) {                                       \

@@ -21,6 +21,8 @@ FusedKernel fused_kernel_occ8(bool timing);
 
 cudaError_t launch_bind(const LaunchArgs& a, bool zero_feature_times, cudaStream_t st);
 cudaError_t launch_fused(const LaunchArgs& a, int occupancy, bool timing, int grid, size_t smem_bytes, cudaStream_t st);
+// eb_warp_kernel: pools the `warp_features` features on the warp-per-bag schedule (one CTA per 8 bags).
+cudaError_t launch_warp(const LaunchArgs& a, bool timing, int warp_features, cudaStream_t st);
 cudaError_t fused_ctas_per_sm(int occupancy, size_t smem_bytes, int* per_sm);
 cudaError_t launch_place(const float* src, float* dst, int64_t rows, int64_t dst_ld, int num_segments,
                          const void* segments, int vec_ok, cudaStream_t st);

@@ -1,0 +1,180 @@
+// eb_warp_kernel: the warp-per-bag schedule (EB_SCHED_WARP) as a kernel of its own.
+//
+// Long, evenly sized bags over tables whose hot rows sit in L1/L2 are bound by instruction count and by L1
+// throughput, and register spills travel through that same L1.  The loop below is therefore as lean as the
+// reference's ws::SparseSegmentReduceCore (examples/csrc/include/warp_per_sample_kernel.cuh:48-60: about 11
+// instructions per 512-byte row at 32 registers): scalars only, no votes, no zero-filled buffers.  It lives in its
+// own kernel, built for 8 CTAs per SM, because inside the fused kernel it degraded the register allocation of
+// every other schedule (and theirs degraded its own), and as a plain grid (one CTA per 8 consecutive bags of a
+// feature, found through the second prefix sum the binding kernel writes) because tickets, chunks and tile
+// state cost registers that the row buffers need.  Input sanitising (per bag) and output addressing (single
+// matrix or peers) follow eb_fused_kernel.
+#pragma once
+#include "eb_common.cuh"
+#include "eb_schedules.cuh"
+
+namespace ebk {
+
+template <int V>
+struct AccPack {
+  float v[V];
+};
+
+// vp points at this slot's first entry; the slot owns vp[0], vp[stride], vp[2 * stride], ...: `n_full`
+// macro-steps of U entries, then `tail` (< U) more.  A lane whose indices are all valid loads unconditionally; a
+// lane that meets a bad index takes the careful branch on its own (no warp-wide vote).
+template <typename T, int V, int U, bool IDX64>
+__device__ __forceinline__ AccPack<V> bag_sum(const typename IdxOf<IDX64>::type* vp, const char* tcol,
+                                              unsigned row_bytes, unsigned long long rows, int stride, int n_full,
+                                              int tail, uint32_t* status) {
+  using Ops = RowOps<T, V>;
+  using IdxT = typename IdxOf<IDX64>::type;
+  AccPack<V> a;
+  zero_vals<V>(a.v);
+  const unsigned rows32 = rows > 0x80000000ull ? 0x80000000u : (unsigned)rows;
+  for (int i = 0; i < n_full; ++i) {
+    IdxT idx[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) idx[u] = __ldg(vp + u * stride);
+    vp += U * stride;
+    bool valid = true;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if constexpr (IDX64) valid = valid && (unsigned long long)idx[u] < rows;
+      else valid = valid && (unsigned)idx[u] < rows32;
+    }
+    if (valid) {
+      typename Ops::Raw rows_[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if constexpr (IDX64) rows_[u] = Ops::load(tcol + idx[u] * (long long)row_bytes);
+        else rows_[u] = Ops::load(tcol + (unsigned long long)(unsigned)idx[u] * row_bytes);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) Ops::add(a.v, rows_[u]);
+    } else {
+      flag(status, kStatusBadIndex);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        bool ok;
+        if constexpr (IDX64) ok = (unsigned long long)idx[u] < rows;
+        else ok = (unsigned)idx[u] < rows32;
+        if (ok) {
+          if constexpr (IDX64) Ops::add(a.v, Ops::load(tcol + idx[u] * (long long)row_bytes));
+          else Ops::add(a.v, Ops::load(tcol + (unsigned long long)(unsigned)idx[u] * row_bytes));
+        }
+      }
+    }
+  }
+  for (int u = 0; u < tail; ++u) {  // ragged end of the bag, one entry at a time
+    const IdxT ix = __ldg(vp + u * stride);
+    bool ok;
+    if constexpr (IDX64) ok = (unsigned long long)ix < rows;
+    else ok = (unsigned)ix < rows32;
+    if (ok) {
+      if constexpr (IDX64) Ops::add(a.v, Ops::load(tcol + ix * (long long)row_bytes));
+      else Ops::add(a.v, Ops::load(tcol + (unsigned long long)(unsigned)ix * row_bytes));
+    } else {
+      flag(status, kStatusBadIndex);
+    }
+  }
+  return a;
+}
+
+// One bag, one warp.
+template <typename T, int V, int U, bool IDX64>
+__device__ __forceinline__ void bag_warp(const FeatStatic& fs, const char* values, int64_t s, int64_t e, float* orow,
+                                         int out_vec, uint32_t* status, int lane) {
+  const int lgG = fs.lg_group, G = 1 << lgG, R = 32 >> lgG;
+  const int r = lane >> lgG, cl = lane & (G - 1);
+  const int len = (int)(e - s);
+  const int n_full = len / (R * U);           // macro-steps in which every slot has U entries
+  const int left = len - n_full * R * U - r;  // entries left from my first tail position on
+  const int tail = left <= 0 ? 0 : (left + R - 1) / R;
+  const typename IdxOf<IDX64>::type* vp = reinterpret_cast<const typename IdxOf<IDX64>::type*>(values) + s + r;
+  for (int xc = 0; xc < fs.nx; ++xc) {
+    const int cs = (xc * G + cl) * V;
+    const bool col_ok = cs < fs.dim;
+    AccPack<V> a;
+    if (col_ok) {
+      a = bag_sum<T, V, U, IDX64>(vp, fs.table + (size_t)cs * sizeof(T), (unsigned)fs.row_bytes,
+                                  (unsigned long long)fs.rows, R, n_full, tail, status);
+    } else {
+      zero_vals<V>(a.v);
+    }
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      if (d >= G) {
+#pragma unroll
+        for (int k = 0; k < V; ++k) a.v[k] += __shfl_xor_sync(kFull, a.v[k], d);
+      }
+    }
+    if (r == 0 && col_ok) store_vals<V>(orow + cs, a.v, out_vec);  // an empty bag stores zeros
+  }
+}
+
+constexpr int kWarpKernelOccupancy = 8;
+
+// Plain grid: CTA t pools 8 consecutive bags (one per warp) of the feature that the binding kernel's second
+// prefix sum maps t to.  Nothing else is alive in a warp besides its bag: no tickets, no chunks.
+template <bool TIMING>
+__global__ void __launch_bounds__(kCtaThreads, kWarpKernelOccupancy) eb_warp_kernel(LaunchArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int F = a.num_features;
+  const WsLayout L = ws_layout(F);
+  WsHeader* hdr = reinterpret_cast<WsHeader*>(a.ws + L.header);
+  const int32_t* prefix = reinterpret_cast<const int32_t*>(a.ws + L.cta_prefix);
+  const uint32_t t = blockIdx.x;
+  if (t >= hdr->cta_tiles) return;
+  int lo = 0, hi = F;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if ((uint32_t)__ldg(prefix + mid) <= t) lo = mid; else hi = mid;
+  }
+  const int f = __ldg(reinterpret_cast<const int32_t*>(a.ws + L.order) + lo);
+  const int64_t bag = (int64_t)(t - (uint32_t)__ldg(prefix + lo)) * kWarpsPerCta + (threadIdx.x >> 5);
+  if (bag >= a.batch) return;
+  const FeatStatic fs = a.feats[f];
+  const FeatDyn fd = reinterpret_cast<const FeatDyn*>(a.ws + L.dyn)[f];
+  long long c0 = 0;
+  if (TIMING) c0 = clock64();
+
+  // this bag's entries, forced inside [0, nnz] and non-negative in length
+  const bool idx64 = a.idx64 != 0;
+  int64_t s = load_index(fd.offsets, bag, idx64);
+  int64_t e = (!a.has_end && bag + 1 >= a.batch) ? fd.nnz : load_index(fd.offsets, bag + 1, idx64);
+  const int64_t s0 = s, e0 = e;
+  s = clamp_off(s, fd.nnz);
+  e = clamp_off(e, fd.nnz);
+  if (e < s) e = s;
+  if (e - s > 0x3fffffff) e = s + 0x3fffffff;
+  if ((s != s0 || e != e0) && lane == 0) flag(&hdr->status, kStatusBadOffsets);
+
+  float* orow;
+  if (a.rows_per_peer == 0) {
+    orow = a.out + bag * a.out_ld + fs.col_off;
+  } else {
+    const int64_t d = bag / a.rows_per_peer;
+    orow = hdr->peer_out[d] + (bag - d * a.rows_per_peer) * a.out_ld + fs.col_off;
+  }
+  const int out_vec = (a.out_vec == 2 && (fs.col_off & 7) == 0) ? 2 : ((a.out_vec != 0 && (fs.col_off & 3) == 0) ? 1 : 0);
+  uint32_t* status = &hdr->status;
+  const bool u2 = fs.unroll <= 2;  // two or four rows per lane in flight
+  if (idx64) {
+    if (fs.dtype == 1) bag_warp<__half, 8, 2, true>(fs, fd.values, s, e, orow, out_vec, status, lane);
+    else bag_warp<float, 4, 2, true>(fs, fd.values, s, e, orow, out_vec, status, lane);
+  } else if (fs.dtype == 1) {
+    if (u2) bag_warp<__half, 8, 2, false>(fs, fd.values, s, e, orow, out_vec, status, lane);
+    else bag_warp<__half, 8, 4, false>(fs, fd.values, s, e, orow, out_vec, status, lane);
+  } else {
+    if (u2) bag_warp<float, 4, 2, false>(fs, fd.values, s, e, orow, out_vec, status, lane);
+    else bag_warp<float, 4, 4, false>(fs, fd.values, s, e, orow, out_vec, status, lane);
+  }
+  if (TIMING) {
+    __syncwarp();
+    const long long c1 = clock64();
+    if (lane == 0) atomicAdd(reinterpret_cast<unsigned long long*>(a.ws + L.feat_ns) + f, (unsigned long long)(c1 - c0));
+  }
+}
+
+}  // namespace ebk

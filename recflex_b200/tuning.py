@@ -150,10 +150,12 @@ class Tuner:
             for u in self.config.unrolls:
                 if kind == "group" and st.mean_len > 64:
                     continue  # a slot walking hundreds of rows alone leaves the other slots idle
-                if kind in ("warp", "group") and u > 1 and st.max_len <= 1:
+                if kind == "group" and u > 1 and st.max_len <= 1:
                     continue  # one-hot: a bag never has a second row to keep in flight
                 if kind == "pipe" and u == 1:
                     continue  # the ring's shallowest variant is unroll 2
+                if kind == "warp" and u not in (2, 4):
+                    continue  # the warp-per-bag kernel keeps two or four rows per lane in flight
                 cands.append(Schedule(kind, u))
         return cands
 

@@ -37,10 +37,10 @@ def test_tuner_end_to_end(tmp_path):
     res.save(path, workload=cfg.name)
     back = TuneResult.load(path)
     assert back.schedules == res.schedules and back.occupancy == res.occupancy
-    # one-hot features never get a multi-row unroll from warp/group candidates
+    # one-hot features never get a multi-row unroll from the slot-per-bag candidates
     onehot = [f for f, fs in enumerate(cfg.features) if fs.length == "onehot"]
     for f in onehot:
-        assert all(not (c.kind in (1, 2) and c.unroll > 1) for c in tuner.candidates(f))
+        assert all(not (c.kind == 1 and c.unroll > 1) for c in tuner.candidates(f))
     # mutation validation: every mutation is timed, the pick is one of them
     times, pick = tuner.mutation_validation(res, onehot[0])
     assert len(times) == len(tuner.candidates(onehot[0])) and all(t > 0 for t in times)
