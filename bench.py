@@ -64,6 +64,9 @@ def parse_args():
                    help="sharded workloads on ONE GPU: build only rank --emulate-rank's shard of a sharding over this "
                         "many ranks and time its pooling alone (no exchange); for profiling a shard")
     p.add_argument("--emulate-rank", type=int, default=0)
+    p.add_argument("--compare-batch-order", action="store_true",
+                   help="sharded path, peer exchange: also time the steps with tiles walked in batch order "
+                        "(destination interleave off) and report that time beside the headline")
     p.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
                    help="sharded path: fused peer-memory stores, or pool + NCCL all-to-all + placement")
     return p.parse_args()
@@ -541,6 +544,23 @@ def run_sharded(args):
     if mod.local is not None:
         mod.local.kernel_timing(False)
 
+    t_plain = 0.0
+    if args.compare_batch_order and args.exchange == "peer":
+        if mod.local is not None:
+            mod.local.set_peer_interleave(False)
+        for i in range(3):
+            run_step(*devb[i % nb])
+        barrier()
+        ev4, ev5 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev4.record()
+        for i in range(K):
+            run_step(*devb[i % nb])
+        ev5.record()
+        barrier()
+        t_plain = ev4.elapsed_time(ev5) * 1e-3
+        if mod.local is not None:
+            mod.local.set_peer_interleave(True)
+
     t_e2e = None
     if not args.no_e2e:
         def e2e_step(i):
@@ -562,7 +582,8 @@ def run_sharded(args):
 
     launches_per_step = 1 if args.exchange == "peer" else args.chunks
     k_sum = sum(ktimes) / max(1, min(K, 256 // launches_per_step)) if ktimes else 0.0  # pooled-kernel ms per step, this rank
-    stats = torch.tensor([t_dev, t_e2e or 0.0, k_sum, float(sum(alg) / len(alg))], dtype=torch.float64, device=dev)
+    stats = torch.tensor([t_dev, t_e2e or 0.0, k_sum, float(sum(alg) / len(alg)), t_plain], dtype=torch.float64,
+                         device=dev)
     mx = stats.clone()
     dist.all_reduce(mx, op=dist.ReduceOp.MAX)
     sm = stats.clone()
@@ -570,7 +591,7 @@ def run_sharded(args):
     if rank == 0:
         peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
         peak = float(json.load(open(peaks_path))["hbm_gbs"]) if os.path.exists(peaks_path) else 6650.0
-        t_dev, t_e2e_m, k_max, _ = [float(x) for x in mx]
+        t_dev, t_e2e_m, k_max, _, t_plain_m = [float(x) for x in mx]
         total_alg = float(sm[3])
         h2d = sum(t.numel() * 4 for t in host[0][0]) + sum(t.numel() * 4 for t in host[0][1])
         exch = (world - 1) / world * B * cfg.output_units * 4 / world  # bytes each rank sends per step (mean)
@@ -601,6 +622,8 @@ def run_sharded(args):
             "gpu_launches": K * (2 if args.exchange == "peer" else args.chunks * 3),
             "clocks": sampler.summary(),
         }
+        if t_plain_m:
+            line["config"]["batch_order_ms_per_step"] = t_plain_m / K * 1e3
         print(json.dumps(line), flush=True)
     dist.barrier()
     if args.exchange == "peer":

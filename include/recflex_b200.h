@@ -260,6 +260,15 @@ int eb_forward_peers(eb_handle* h, int64_t batch, const void* const* values_ptrs
                      void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Order in which eb_forward_peers walks the batch (no counterpart in the
+ * reference).  enabled != 0 (the default): consecutive tiles of a feature are
+ * dealt round-robin over the destination ranks, so that every GPU of the node
+ * stores to all the others at any moment.  0: batch order, i.e. rank 0's rows
+ * first on every GPU.  The results are the same either way.
+ */
+int eb_set_peer_interleave(eb_handle* h, int enabled);
+
+/*
  * Device buffers other processes of this node can map (CUDA IPC): eb_peer_alloc
  * allocates `bytes` on `device` and fills a 64-byte handle to send to the other
  * ranks; eb_peer_open maps a peer's handle into this process (the returned

@@ -84,6 +84,7 @@ struct eb_handle {
   bool ev_used[kRing] = {};
   int ring_pos = 0;
   // optional event pairs around the fused-kernel launches
+  bool peer_interleave = true;  // eb_forward_peers deals tiles round-robin over the destination ranks
   int warp_features = 0;   // features pooled by eb_warp_kernel (warp-per-bag schedule, vector path)
   size_t smem_bytes = 0;   // dynamic shared memory of the fused kernel (the pipelined schedule's rings)
   bool time_kernels = false;
@@ -426,8 +427,15 @@ int eb_forward_peers(eb_handle* h, int64_t batch, const void* const* values_ptrs
   LaunchArgs a = make_args(h, batch, index_dtype, offsets_have_end, peer_out[0], out_ld, workspace);
   a.out_vec = vec;
   a.rows_per_peer = batch / world;
+  a.peer_spread = h->peer_interleave ? world : 0;
   for (int r = 0; r < world; ++r) a.peer_out[r] = peer_out[r];
   return run(h, a, false, st);
+}
+
+int eb_set_peer_interleave(eb_handle* h, int enabled) {
+  if (!h) return fail(EB_ERR_INVALID_ARG, "null handle");
+  h->peer_interleave = enabled != 0;
+  return EB_OK;
 }
 
 int eb_peer_alloc(int device, size_t bytes, void** ptr, unsigned char* handle64) {

@@ -98,10 +98,22 @@ struct LaunchArgs {
   int32_t out_vec;        // out base and out_ld allow 16-byte (1) or 32-byte (2) stores
   int32_t warps_total;    // persistent warps of the fused kernel (for tile sizing)
   int32_t ring_bytes;     // shared memory per warp for the pipelined schedule's ring (0 when no feature uses it)
-  int32_t pad_;
+  int32_t peer_spread;    // peer mode: number of ranks to deal a feature's consecutive tiles over (0 = batch order)
   // peer mode (rows_per_peer > 0): sample b is stored to peer_out[b / rows_per_peer], row b % rows_per_peer
   int64_t rows_per_peer;
   float* peer_out[kMaxPeers];
 };
+
+// Peer mode: which slice of the batch the i-th tile (of `n` bags) of a feature pools.  In batch order every
+// GPU of the node would store to rank 0's rows first, then rank 1's, ...: the receivers' links take turns being
+// oversubscribed.  Dealing consecutive tiles round-robin over the destination ranks keeps all links busy at once.
+// The mapping is a bijection on [0, batch / n); it needs tiles that do not straddle two ranks' rows.
+__host__ __device__ inline int64_t spread_tile(int64_t tile, int n, int world, int64_t rows_per_peer) {
+  if (world <= 1 || rows_per_peer <= 0 || rows_per_peer > 0x7fffffff) return tile;
+  const uint32_t rpp = (uint32_t)rows_per_peer, per_peer = rpp / (uint32_t)n;
+  if (per_peer * (uint32_t)n != rpp) return tile;
+  const uint32_t i = (uint32_t)tile, w = (uint32_t)world;
+  return (int64_t)(i % w) * per_peer + i / w;
+}
 
 }  // namespace ebk

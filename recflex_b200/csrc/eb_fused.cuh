@@ -110,10 +110,11 @@ __global__ void __launch_bounds__(kCtaThreads, OCC) eb_fused_kernel(LaunchArgs a
       if ((uint32_t)__ldg(tile_prefix + mid) <= t) lo = mid; else hi = mid;
     }
     const int f = __ldg(order + lo);
-    const int64_t tile = (int64_t)(t - (uint32_t)__ldg(tile_prefix + lo));
+    int64_t tile = (int64_t)(t - (uint32_t)__ldg(tile_prefix + lo));
     const FeatStatic fs = a.feats[f];
     const FeatDyn fd = dyn[f];
     const int n = __ldg(bpt + f);
+    if (a.peer_spread) tile = spread_tile(tile, n, a.peer_spread, a.rows_per_peer);
     const int64_t b0 = tile * n;
     const int64_t b1 = (b0 + n) < a.batch ? (b0 + n) : a.batch;
 

@@ -132,7 +132,9 @@ __global__ void __launch_bounds__(kCtaThreads, kWarpKernelOccupancy) eb_warp_ker
     if ((uint32_t)__ldg(prefix + mid) <= t) lo = mid; else hi = mid;
   }
   const int f = __ldg(reinterpret_cast<const int32_t*>(a.ws + L.order) + lo);
-  const int64_t bag = (int64_t)(t - (uint32_t)__ldg(prefix + lo)) * kWarpsPerCta + (threadIdx.x >> 5);
+  int64_t tile = (int64_t)(t - (uint32_t)__ldg(prefix + lo));
+  if (a.peer_spread) tile = spread_tile(tile, kWarpsPerCta, a.peer_spread, a.rows_per_peer);
+  const int64_t bag = tile * kWarpsPerCta + (threadIdx.x >> 5);
   if (bag >= a.batch) return;
   const FeatStatic fs = a.feats[f];
   const FeatDyn fd = reinterpret_cast<const FeatDyn*>(a.ws + L.dyn)[f];

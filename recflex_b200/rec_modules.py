@@ -225,6 +225,11 @@ class FeatEmbed(nn.Module):
         _lib.check(self._lib.eb_set_output_columns(self._h, arr, int(units)))
         self.output_units = int(units)
 
+    def set_peer_interleave(self, enabled: bool) -> None:
+        """forward_peers deals a feature's consecutive tiles round-robin over the destination ranks (default) or
+        walks the batch in order (False).  Same results; only the NVLink traffic pattern changes."""
+        _lib.check(self._lib.eb_set_peer_interleave(self._h, 1 if enabled else 0))
+
     def forward_peers(self, values: Sequence[torch.Tensor], offsets: Sequence[torch.Tensor],
                       peer_ptrs: Sequence[int], out_ld: int) -> None:
         """Fused pooling + exchange: sample b goes to the output matrix of rank b // (batch / world) whose

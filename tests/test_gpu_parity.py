@@ -329,3 +329,34 @@ def test_long_bags(kind, idt):
     good = [v.copy() for v in values]
     expect = oracle.pool(tables, bad, offsets, acc64=True, strict=False)  # the oracle skips the bad entry too
     np.testing.assert_allclose(out.cpu().numpy(), expect, rtol=2e-3, atol=2e-5)
+
+
+@pytest.mark.parametrize("kind", KINDS)
+@pytest.mark.parametrize("interleave", [True, False])
+def test_peer_mode_on_one_device(kind, interleave):
+    """eb_forward_peers with every rank's output matrix on this GPU: sample b must land in matrix b // rows at row
+    b % rows, whether a feature's tiles are dealt round-robin over the destinations or walked in batch order."""
+    world, rows = 4, 512
+    cfg, tables, values, offsets = small_model(2, 0.01, world * rows)
+    mod = FeatEmbed("cuda:0", embed_tables=device_tables(tables))
+    mod.set_schedules(all_schedules(kind, 4, len(tables)))
+    mod.set_peer_interleave(interleave)
+    units = mod.output_units
+    outs = [torch.full((rows, units), float("nan"), device="cuda:0") for _ in range(world)]
+    mod.forward_peers(to_device(values), to_device(offsets), [o.data_ptr() for o in outs], units)
+    torch.cuda.synchronize()
+    mod.check_status()
+    check_against_oracle(torch.cat(outs), tables, values, offsets, "f32")
+
+
+def test_peer_mode_with_tiles_wider_than_a_rank():
+    """Tiles that straddle two ranks' rows (bags_per_tile does not divide batch / world) keep batch order."""
+    world, rows = 4, 96
+    cfg, tables, values, offsets = small_model(1, 1.0, world * rows)
+    mod = FeatEmbed("cuda:0", embed_tables=device_tables(tables))
+    mod.set_schedules(all_schedules("stream", 4, len(tables), bags_per_tile=64))
+    units = mod.output_units
+    outs = [torch.full((rows, units), float("nan"), device="cuda:0") for _ in range(world)]
+    mod.forward_peers(to_device(values), to_device(offsets), [o.data_ptr() for o in outs], units)
+    torch.cuda.synchronize()
+    check_against_oracle(torch.cat(outs), tables, values, offsets, "f32")

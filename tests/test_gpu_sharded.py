@@ -23,6 +23,6 @@ def test_sharded_forward_fused_peer_exchange():
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
     world = 4 if n >= 4 else 2
-    res = run_workers(world, "nccl", ["--exchange", "peer", "--batch", str(world * 64)])
+    res = run_workers(world, "nccl", ["--exchange", "peer", "--batch", str(world * 1024)])
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
     assert f"sharded ok nccl world {world}" in res.stdout
