@@ -53,6 +53,7 @@ class TuneConfig:
     max_probe_bytes: int = 2 << 30  # cap of the local stage's output buffer
     uniform_portfolio: Sequence[Tuple[str, int]] = (("stream", 2), ("stream", 4), ("stream", 8), ("warp", 4),
                                                     ("pipe", 2), ("pipe", 4), ("pipe", 8))
+    hybrid_min_len: Sequence[int] = (32, 128)  # warp-per-bag kernel for features whose mean bag is at least this long
     refine_top: int = 3           # local-stage candidates tried per cluster in the refinement pass (0 = off)
     refine_min_gain: float = 0.003  # a switch must make the fused kernel this much faster (relative) to be kept
 
@@ -243,11 +244,26 @@ class Tuner:
                 scheds.append(feat_cands[f][min(range(len(t)), key=t.__getitem__)])
             winners[occ] = scheds
             global_ms[occ] = self.fused_ms(scheds, occ)
+            best_uni, best_uni_ms = None, float("inf")
             for kind, unroll in self.config.uniform_portfolio:  # never end up worse than a uniform assignment
                 uni = [Schedule(kind, unroll) for _ in range(self.num_feats)]
                 ms = self.fused_ms(uni, occ)
                 if ms < global_ms[occ]:
                     global_ms[occ], winners[occ] = ms, uni
+                if kind != "warp" and ms < best_uni_ms:
+                    best_uni, best_uni_ms = uni, ms
+            # long bags to the warp-per-bag kernel, everything else on the best uniform schedule of the fused kernel:
+            # the local stage ranks a feature's candidates inside ONE kernel and cannot see this split
+            for min_len in self.config.hybrid_min_len:
+                long_bags = [f for f in range(self.num_feats) if self.stats[f].mean_len >= min_len]
+                if best_uni is None or not long_bags or len(long_bags) == self.num_feats:
+                    continue
+                mix = list(best_uni)
+                for f in long_bags:
+                    mix[f] = Schedule("warp", 4)
+                ms = self.fused_ms(mix, occ)
+                if ms < global_ms[occ]:
+                    global_ms[occ], winners[occ] = ms, mix
         best = min(global_ms, key=global_ms.get)
         self.module.set_schedules(winners[best], occupancy=best)
         return TuneResult(winners[best], best, local, global_ms, self.stats)
