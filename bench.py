@@ -53,6 +53,9 @@ def parse_args():
     p.add_argument("--batches", type=int, default=4, help="distinct batches rotated through the steps")
     p.add_argument("--schedules", type=str, default="", help="JSON file written by the tuner (default: tuned/<workload>.json if present)")
     p.add_argument("--occupancy", type=int, default=0)
+    p.add_argument("--overlap", type=int, default=-1,
+                   help="CTAs per SM of the fused kernel while the warp-per-bag kernel runs beside it (0 = one after "
+                        "the other; default: the tuned file's value, else 0)")
     p.add_argument("--kind", type=str, default="", help="force one schedule kind for every feature (debugging)")
     p.add_argument("--unroll", type=int, default=0)
     p.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU baseline budget")
@@ -230,7 +233,7 @@ def run_ours(args):
     import torch
     import torch.distributed as dist
 
-    from recflex_b200 import synth
+    from recflex_b200 import _lib, synth
     from recflex_b200.rec_modules import FeatEmbed, Schedule
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -270,6 +273,12 @@ def run_ours(args):
     elif args.occupancy:
         mod.set_schedules(None, occupancy=args.occupancy)
     _, occupancy = mod.get_schedules()
+    overlap = args.overlap
+    if overlap < 0:
+        overlap = int(tuned.get("overlap", 0)) if sched_note.startswith("tuned (") else 0
+    if overlap:
+        mod.set_kernel_overlap(overlap)
+        sched_note += f"; warp-per-bag kernel beside the fused kernel ({overlap} CTAs/SM)"
 
     # distinct batches, different on every rank; kept packed on the host (pinned) and on the device
     host_v, host_o, dev_v, dev_o, alg_bytes = [], [], [], [], []
@@ -294,11 +303,15 @@ def run_ours(args):
         tb = [([torch.from_numpy(v).to(dev) for v in first[0]], [torch.from_numpy(o).to(dev) for o in first[1]])]
         res = Tuner(mod, tb, TuneConfig()).tune()
         sched_note = f"tuned before timing (occupancy {res.occupancy})"
+        overlap = res.overlap
+        if overlap:
+            sched_note += f"; warp-per-bag kernel beside the fused kernel ({overlap} CTAs/SM)"
         if args.schedules:
             res.save(args.schedules, workload=cfg.name)
         del tb
         _, occupancy = mod.get_schedules()
 
+    per_step_launches = 2 + (1 if any(s.kind == _lib.EB_SCHED_WARP for s in mod.get_schedules()[0]) else 0)
     for i in range(max(3, args.warmup)):
         mod.forward_packed(dev_v[i % nb], dev_o[i % nb], out=out)
     mod.check_status()
@@ -329,6 +342,8 @@ def run_ours(args):
         mod_b = FeatEmbed(dev, embed_tables=tables)
         scheds, occ_b = mod.get_schedules()
         mod_b.set_schedules(scheds, occupancy=occ_b)
+        if overlap:
+            mod_b.set_kernel_overlap(overlap)
         lanes = [(mod, torch.cuda.Stream(device=dev), host_out),
                  (mod_b, torch.cuda.Stream(device=dev), torch.empty_like(host_out).pin_memory())]
 
@@ -393,7 +408,8 @@ def run_ours(args):
             },
             "e2e": {"value": world * K * B / t_e2e if t_e2e else None, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": t_e2e / K * 1e3 if t_e2e else None},
-            "gpu_launches": 2 * K + (2 * K if t_e2e else 0),
+            # binding kernel + fused kernel per step, + the warp-per-bag kernel when a feature is on that schedule
+            "gpu_launches": per_step_launches * K + (per_step_launches * K if t_e2e else 0),
             "clocks": sampler.summary(),
         }
         if world == 1 and not args.no_cpu_baseline:

@@ -260,6 +260,19 @@ int eb_forward_peers(eb_handle* h, int64_t batch, const void* const* values_ptrs
                      void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Overlap of the two pooling kernels (no counterpart in the reference, whose
+ * single generated kernel holds every schedule).  0 (the default): features on
+ * EB_SCHED_WARP are pooled by their own kernel, then the fused kernel pools the
+ * rest, both on the caller's stream.  n > 0: the fused kernel is launched first
+ * on n CTAs per SM (never more than the occupancy given to eb_set_schedules)
+ * and the warp-per-bag kernel runs beside it on a stream the handle owns,
+ * forked from and joined back into the caller's stream with events, so the
+ * caller sees the usual stream order.  Only used when some, but not all,
+ * features are on EB_SCHED_WARP; eb_forward_timed keeps the serial order.
+ */
+int eb_set_kernel_overlap(eb_handle* h, int fused_ctas_per_sm);
+
+/*
  * Order in which eb_forward_peers walks the batch (no counterpart in the
  * reference).  enabled != 0 (the default): consecutive tiles of a feature are
  * dealt round-robin over the destination ranks, so that every GPU of the node

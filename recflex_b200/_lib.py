@@ -77,6 +77,7 @@ PROTOTYPES = {
                                    C.POINTER(C.c_int64), C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_int, C.c_int64,
                                    C.c_void_p, C.c_size_t, C.c_void_p]),
     "eb_set_peer_interleave": (C.c_int, [C.c_void_p, C.c_int]),
+    "eb_set_kernel_overlap": (C.c_int, [C.c_void_p, C.c_int]),
     "eb_peer_alloc": (C.c_int, [C.c_int, C.c_size_t, C.POINTER(C.c_void_p), C.c_void_p]),
     "eb_peer_open": (C.c_int, [C.c_int, C.c_void_p, C.POINTER(C.c_void_p)]),
     "eb_peer_close": (C.c_int, [C.c_int, C.c_void_p]),

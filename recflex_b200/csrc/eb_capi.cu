@@ -84,6 +84,9 @@ struct eb_handle {
   bool ev_used[kRing] = {};
   int ring_pos = 0;
   // optional event pairs around the fused-kernel launches
+  int overlap_ctas = 0;         // > 0: fused kernel on this many CTAs per SM with eb_warp_kernel beside it (see run())
+  cudaStream_t side = nullptr;  // stream of the warp-per-bag kernel in overlap mode
+  cudaEvent_t fork_ev = nullptr, join_ev = nullptr;
   bool peer_interleave = true;  // eb_forward_peers deals tiles round-robin over the destination ranks
   int warp_features = 0;   // features pooled by eb_warp_kernel (warp-per-bag schedule, vector path)
   size_t smem_bytes = 0;   // dynamic shared memory of the fused kernel (the pipelined schedule's rings)
@@ -168,13 +171,31 @@ LaunchArgs make_args(const eb_handle* h, int64_t batch, int index_dtype, int has
   return a;
 }
 
-int run(eb_handle* h, const LaunchArgs& a, bool timing, cudaStream_t st) {
-  if (a.batch == 0) return EB_OK;
+int run(eb_handle* h, const LaunchArgs& a_in, bool timing, cudaStream_t st) {
+  if (a_in.batch == 0) return EB_OK;
+  LaunchArgs a = a_in;
+  // Overlap mode: long bags over cache-resident tables keep L1 busy, short bags over large tables keep HBM busy,
+  // so the two kernels share the SMs instead of following each other.  The persistent fused kernel goes first on a
+  // reduced grid (it holds its CTA slots until its tickets run out); eb_warp_kernel's plain grid fills the rest of
+  // every SM from a second stream, forked after the binding kernel and joined before anything the caller enqueues
+  // next.  The per-feature timing variant keeps the serial order.
+  const bool overlap = h->overlap_ctas > 0 && h->warp_features > 0 && h->warp_features < h->num_features && !timing;
+  const int ctas_per_sm = overlap && h->overlap_ctas < h->occupancy ? h->overlap_ctas : h->occupancy;
+  a.warps_total = h->sm_count * ctas_per_sm * kWarpsPerCta;
   EB_CUDA(launch_bind(a, timing, st));
   const bool rec = h->time_kernels && h->t_count < kTimeRing;
   if (rec) EB_CUDA(cudaEventRecord(h->t0[h->t_count], st));
-  if (h->warp_features) EB_CUDA(launch_warp(a, timing, h->warp_features, st));
-  EB_CUDA(launch_fused(a, h->occupancy, timing, h->sm_count * h->occupancy, h->smem_bytes, st));
+  if (overlap) {
+    EB_CUDA(cudaEventRecord(h->fork_ev, st));
+    EB_CUDA(launch_fused(a, h->occupancy, timing, h->sm_count * ctas_per_sm, h->smem_bytes, st));
+    EB_CUDA(cudaStreamWaitEvent(h->side, h->fork_ev, 0));
+    EB_CUDA(launch_warp(a, timing, h->warp_features, h->side));
+    EB_CUDA(cudaEventRecord(h->join_ev, h->side));
+    EB_CUDA(cudaStreamWaitEvent(st, h->join_ev, 0));
+  } else {
+    if (h->warp_features) EB_CUDA(launch_warp(a, timing, h->warp_features, st));
+    EB_CUDA(launch_fused(a, h->occupancy, timing, h->sm_count * ctas_per_sm, h->smem_bytes, st));
+  }
   if (rec) {
     EB_CUDA(cudaEventRecord(h->t1[h->t_count], st));
     ++h->t_count;
@@ -296,6 +317,9 @@ int eb_destroy(eb_handle* h) {
     if (h->ev[i]) cudaEventDestroy(h->ev[i]);
     if (h->pinned[i]) cudaFreeHost(h->pinned[i]);
   }
+  if (h->fork_ev) cudaEventDestroy(h->fork_ev);
+  if (h->join_ev) cudaEventDestroy(h->join_ev);
+  if (h->side) cudaStreamDestroy(h->side);
   for (cudaEvent_t e : h->t0) cudaEventDestroy(e);
   for (cudaEvent_t e : h->t1) cudaEventDestroy(e);
   if (h->d_feats) cudaFree(h->d_feats);
@@ -430,6 +454,20 @@ int eb_forward_peers(eb_handle* h, int64_t batch, const void* const* values_ptrs
   a.peer_spread = h->peer_interleave ? world : 0;
   for (int r = 0; r < world; ++r) a.peer_out[r] = peer_out[r];
   return run(h, a, false, st);
+}
+
+int eb_set_kernel_overlap(eb_handle* h, int fused_ctas_per_sm) {
+  if (!h) return fail(EB_ERR_INVALID_ARG, "null handle");
+  if (fused_ctas_per_sm < 0 || fused_ctas_per_sm > kMaxOccupancy)
+    return fail(EB_ERR_INVALID_ARG, "fused_ctas_per_sm must be 0 (off) or 1..%d (got %d)", kMaxOccupancy, fused_ctas_per_sm);
+  if (fused_ctas_per_sm > 0 && !h->side) {
+    DeviceGuard guard(h->device);
+    EB_CUDA(cudaStreamCreateWithFlags(&h->side, cudaStreamNonBlocking));
+    EB_CUDA(cudaEventCreateWithFlags(&h->fork_ev, cudaEventDisableTiming));
+    EB_CUDA(cudaEventCreateWithFlags(&h->join_ev, cudaEventDisableTiming));
+  }
+  h->overlap_ctas = fused_ctas_per_sm;
+  return EB_OK;
 }
 
 int eb_set_peer_interleave(eb_handle* h, int enabled) {

@@ -225,6 +225,11 @@ class FeatEmbed(nn.Module):
         _lib.check(self._lib.eb_set_output_columns(self._h, arr, int(units)))
         self.output_units = int(units)
 
+    def set_kernel_overlap(self, fused_ctas_per_sm: int) -> None:
+        """n > 0: the fused kernel runs on n CTAs per SM and the warp-per-bag kernel beside it on a stream of the
+        handle (joined back into the current stream); 0: one after the other on the current stream (default)."""
+        _lib.check(self._lib.eb_set_kernel_overlap(self._h, int(fused_ctas_per_sm)))
+
     def set_peer_interleave(self, enabled: bool) -> None:
         """forward_peers deals a feature's consecutive tiles round-robin over the destination ranks (default) or
         walks the batch in order (False).  Same results; only the NVLink traffic pattern changes."""

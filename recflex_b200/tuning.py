@@ -33,6 +33,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
+from . import _lib
 from .rec_modules import FeatEmbed, Schedule
 
 KINDS = ("group", "warp", "flat", "stream", "pipe")
@@ -54,6 +55,7 @@ class TuneConfig:
     uniform_portfolio: Sequence[Tuple[str, int]] = (("stream", 2), ("stream", 4), ("stream", 8), ("warp", 4),
                                                     ("pipe", 2), ("pipe", 4), ("pipe", 8))
     hybrid_min_len: Sequence[int] = (32, 128)  # warp-per-bag kernel for features whose mean bag is at least this long
+    overlaps: Sequence[int] = (1, 2, 3)  # fused-kernel CTAs per SM tried with the warp-per-bag kernel beside it
     refine_top: int = 3           # local-stage candidates tried per cluster in the refinement pass (0 = off)
     refine_min_gain: float = 0.003  # a switch must make the fused kernel this much faster (relative) to be kept
 
@@ -77,10 +79,12 @@ class TuneResult:
     local_times: Dict[int, Dict[int, List[float]]] = field(default_factory=dict)   # feature -> occupancy -> per candidate
     global_ms: Dict[int, float] = field(default_factory=dict)                       # occupancy -> fused-kernel ms
     stats: List[InputStats] = field(default_factory=list)
+    overlap: int = 0   # > 0: fused kernel on this many CTAs per SM, warp-per-bag kernel beside it (set_kernel_overlap)
 
     def to_json(self) -> dict:
         return {
             "occupancy": self.occupancy,
+            "overlap": self.overlap,
             "schedules": [s.to_json() for s in self.schedules],
             "global_ms": {str(k): v for k, v in self.global_ms.items()},
             "stats": [[s.mean_len, s.max_len, s.empty_frac] for s in self.stats],
@@ -101,6 +105,7 @@ class TuneResult:
             occupancy=int(d["occupancy"]),
             global_ms={int(k): float(v) for k, v in d.get("global_ms", {}).items()},
             stats=[InputStats(*s) for s in d.get("stats", [])],
+            overlap=int(d.get("overlap", 0)),
         )
 
 
@@ -302,8 +307,30 @@ class Tuner:
         gm[occ] = best_ms
         return TuneResult(scheds, occ, result.local_times, gm, result.stats)
 
+    def tune_overlap(self, result: TuneResult) -> TuneResult:
+        """Last step: when the assignment uses both kernels (some features on the warp-per-bag schedule, some not),
+        try running them side by side, the fused kernel on a reduced grid, and keep the fastest arrangement."""
+        mod = self.module
+        n_warp = sum(1 for s in result.schedules if s.kind == _lib.EB_SCHED_WARP)
+        mod.set_kernel_overlap(0)
+        if n_warp == 0 or n_warp == self.num_feats or not self.config.overlaps:
+            return result
+        best_n, best_ms = 0, self.fused_ms(result.schedules, result.occupancy)
+        for n in self.config.overlaps:
+            if n > result.occupancy:
+                continue
+            mod.set_kernel_overlap(n)
+            ms = self.fused_ms(result.schedules, result.occupancy)
+            if ms < best_ms * (1.0 - self.config.refine_min_gain):
+                best_n, best_ms = n, ms
+        mod.set_kernel_overlap(best_n)
+        gm = dict(result.global_ms)
+        gm[result.occupancy] = best_ms
+        return TuneResult(result.schedules, result.occupancy, result.local_times, gm, result.stats, best_n)
+
     def tune(self) -> TuneResult:
-        return self.refine(self.solve(self.tune_local()))
+        self.module.set_kernel_overlap(0)
+        return self.tune_overlap(self.refine(self.solve(self.tune_local())))
 
     # -- ablations ---------------------------------------------------------
     def mutation_validation(self, result: TuneResult, feat: int) -> Tuple[List[float], int]:

@@ -360,3 +360,30 @@ def test_peer_mode_with_tiles_wider_than_a_rank():
     mod.forward_peers(to_device(values), to_device(offsets), [o.data_ptr() for o in outs], units)
     torch.cuda.synchronize()
     check_against_oracle(torch.cat(outs), tables, values, offsets, "f32")
+
+
+@pytest.mark.parametrize("fused_ctas", [1, 2, 4])
+def test_warp_kernel_beside_the_fused_kernel(fused_ctas):
+    """Overlap mode: features on the warp-per-bag schedule are pooled on the handle's own stream while the fused
+    kernel pools the rest on a reduced grid; results and stream order as seen by the caller do not change."""
+    cfg, tables, values, offsets = small_model(5, 0.01, 2048)
+    mod = FeatEmbed("cuda:0", embed_tables=device_tables(tables))
+    scheds = [Schedule("warp", 4) if f % 3 == 0 else Schedule("pipe" if f % 3 == 1 else "stream", 4)
+              for f in range(len(tables))]
+    mod.set_schedules(scheds, occupancy=4)
+    mod.set_kernel_overlap(fused_ctas)
+    dv, do = to_device(values), to_device(offsets)
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        out = None
+        for _ in range(3):  # back-to-back calls reuse the workspace: each must wait for both kernels of the last
+            out = mod(dv, do)
+        doubled = out * 2.0  # ordered after both kernels through the caller's stream alone
+    st.synchronize()
+    mod.check_status()
+    check_against_oracle(out, tables, values, offsets, "f32")
+    assert torch.equal(doubled, out * 2.0)
+    mod.set_kernel_overlap(0)  # back to one kernel after the other (tile sizes, hence summation order, may differ)
+    again = mod(dv, do)
+    torch.cuda.synchronize()
+    check_against_oracle(again, tables, values, offsets, "f32")

@@ -36,7 +36,8 @@ def test_tuner_end_to_end(tmp_path):
     path = os.path.join(tmp_path, "tuned.json")
     res.save(path, workload=cfg.name)
     back = TuneResult.load(path)
-    assert back.schedules == res.schedules and back.occupancy == res.occupancy
+    assert back.schedules == res.schedules and back.occupancy == res.occupancy and back.overlap == res.overlap
+    assert 0 <= res.overlap <= res.occupancy
     # one-hot features never get a multi-row unroll from the slot-per-bag candidates
     onehot = [f for f, fs in enumerate(cfg.features) if fs.length == "onehot"]
     for f in onehot:
