@@ -421,6 +421,23 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def plan_cfg_shards(cfg, world, cap):
+    """Owner rank per table + summary for the sharded workload: balances what every rank gathers AND what it sends
+    (one-hot features send twice the bytes they gather from an fp16 table), with table bytes kept within 15 % of an
+    even split where that is feasible."""
+    from recflex_b200 import synth
+    from recflex_b200.sharding import plan_shards, shard_summary
+
+    table_bytes = [fs.table_bytes for fs in cfg.features]
+    traffic = synth.expected_traffic(cfg)
+    sent = [cfg.batch * fs.dim * 4 * (world - 1) / world for fs in cfg.features]
+    try:
+        owner = plan_shards(table_bytes, traffic, world, min(cap, int(1.15 * sum(table_bytes) / world)), exchange=sent)
+    except ValueError:
+        owner = plan_shards(table_bytes, traffic, world, cap, exchange=sent)
+    return owner, shard_summary(owner, table_bytes, traffic, world, exchange=sent)
+
+
 def run_shard_emulation(args):
     """One rank's shard of cfg4 on a single GPU: pooling only, for profiling (not a benchmark line of the job)."""
     import torch
@@ -433,8 +450,7 @@ def run_shard_emulation(args):
     torch.cuda.set_device(0)
     cfg = synth.make_config(WORKLOADS[args.workload], row_scale=args.row_scale, batch=args.batch or None)
     W, R, B = args.emulate_world, args.emulate_rank, cfg.batch
-    owner = plan_shards([fs.table_bytes for fs in cfg.features], synth.expected_traffic(cfg), W,
-                        int(torch.cuda.mem_get_info(dev)[1] * 0.88))
+    owner, _ = plan_cfg_shards(cfg, W, int(torch.cuda.mem_get_info(dev)[1] * 0.88))
     local = [f for f, r in enumerate(owner) if r == R]
     mod = FeatEmbed(dev, embed_tables=synth.make_tables_device(cfg, dev, features=local))
     mod.set_schedules(None, occupancy=args.occupancy or 6)
@@ -503,11 +519,10 @@ def run_sharded(args):
                               f"not fit {world} GPU(s) of {total_b / 1e9:.0f} GB", "n_gpus": world}), flush=True)
         dist.destroy_process_group()
         return
-    owner = plan_shards(table_bytes, traffic, world, cap)
-    summ = shard_summary(owner, table_bytes, traffic, world)
+    dims = [fs.dim for fs in cfg.features]
+    owner, summ = plan_cfg_shards(cfg, world, cap)
     local = [f for f, r in enumerate(owner) if r == rank]
     tables = synth.make_tables_device(cfg, dev, features=local)
-    dims = [fs.dim for fs in cfg.features]
     mod = ShardedFeatEmbed(rank, world, owner, dims, local_tables=tables, device=dev, chunks=args.chunks,
                            exchange=args.exchange)
     mod.set_batch_for_empty_rank(B)
@@ -610,7 +625,7 @@ def run_sharded(args):
         t_dev, t_e2e_m, k_max, _, t_plain_m = [float(x) for x in mx]
         total_alg = float(sm[3])
         h2d = sum(t.numel() * 4 for t in host[0][0]) + sum(t.numel() * 4 for t in host[0][1])
-        exch = (world - 1) / world * B * cfg.output_units * 4 / world  # bytes each rank sends per step (mean)
+        exch = max(summ["exchange_per_rank"])  # bytes the busiest rank sends per step
         achieved = (total_alg / world) / (k_max * 1e-3) / 1e9 if k_max else None
         line = {
             "metric": METRIC, "value": K * B / t_dev, "unit": UNIT, "n_gpus": world, "steps": K,
@@ -618,8 +633,9 @@ def run_sharded(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": cfg.name, "features": F, "global_batch": B, "table_dtype": cfg.features[0].dtype,
                        "table_gb_total": round(cfg.table_bytes / 1e9, 1), "output_units": cfg.output_units,
-                       "partitioning": f"table-wise shards over {world} ranks (LPT planner, traffic imbalance "
-                                       f"{summ['traffic_imbalance']:.3f}); exchange: " +
+                       "partitioning": f"table-wise shards over {world} ranks (LPT planner, gather traffic imbalance "
+                                       f"{summ['traffic_imbalance']:.3f}, sent bytes imbalance "
+                                       f"{summ['exchange_imbalance']:.3f}); exchange: " +
                                        ("pooled rows stored by the fused kernel into the destination rank's output "
                                         "over NVLink peer memory, one-element all-reduce as the barrier"
                                         if args.exchange == "peer" else

@@ -38,12 +38,18 @@ from . import _lib
 # planner
 # ---------------------------------------------------------------------------
 def plan_shards(table_bytes: Sequence[int], traffic: Sequence[float], world: int,
-                capacity_bytes: Optional[int] = None) -> List[int]:
+                capacity_bytes: Optional[int] = None, exchange: Optional[Sequence[float]] = None) -> List[int]:
     """Owner rank of every table.
 
     Longest-processing-time greedy on `traffic` (expected gathered bytes per batch: nnz_f * row_bytes_f)
     under a per-rank capacity on `table_bytes`, then pairwise moves/swaps while they lower the maximum
     per-rank traffic.  Raises if the tables do not fit.
+
+    `exchange` (optional: bytes of pooled output each table's owner sends per batch, batch * dim_f * 4 * (world - 1) /
+    world) adds a second load to balance.  One-hot features produce twice as many output bytes as they gather from
+    an fp16 table, so ranks with equal gather traffic can differ by 15 % and more in what they push through NVLink,
+    and at 8 GPUs the exchange, not the pooling, bounds the step.  With it the planner minimises the larger of the
+    two per-rank loads, each measured against its own mean.
     """
     F = len(table_bytes)
     if len(traffic) != F or world < 1:
@@ -51,6 +57,10 @@ def plan_shards(table_bytes: Sequence[int], traffic: Sequence[float], world: int
     cap = capacity_bytes if capacity_bytes is not None else float("inf")
     if any(b > cap for b in table_bytes):
         raise ValueError("a single table exceeds the per-rank capacity")
+    if exchange is not None:
+        if len(exchange) != F:
+            raise ValueError("exchange must have one entry per table")
+        return _plan_two_loads(table_bytes, traffic, exchange, world, cap)
     owner = [-1] * F
     load = [0.0] * world
     used = [0] * world
@@ -96,15 +106,74 @@ def plan_shards(table_bytes: Sequence[int], traffic: Sequence[float], world: int
     return owner
 
 
-def shard_summary(owner: Sequence[int], table_bytes: Sequence[int], traffic: Sequence[float], world: int) -> dict:
+def _plan_two_loads(table_bytes, traffic, exchange, world: int, cap) -> List[int]:
+    """plan_shards with two loads per table: minimise max over ranks of max(gather load, exchange load), each load
+    expressed as a multiple of its per-rank mean."""
+    F = len(table_bytes)
+    na = sum(traffic) / world or 1.0
+    nb = sum(exchange) / world or 1.0
+    a = [t / na for t in traffic]
+    b = [e / nb for e in exchange]
+    owner = [-1] * F
+    A, B, used = [0.0] * world, [0.0] * world, [0] * world
+    for f in sorted(range(F), key=lambda i: (-max(a[i], b[i]), -table_bytes[i])):
+        ranks = [r for r in range(world) if used[r] + table_bytes[f] <= cap]
+        if not ranks:
+            raise ValueError("tables do not fit the per-rank capacity with this greedy order; raise capacity or world")
+        r = min(ranks, key=lambda k: (max(A[k] + a[f], B[k] + b[f]), A[k] + B[k], used[k]))
+        owner[f] = r
+        A[r] += a[f]
+        B[r] += b[f]
+        used[r] += table_bytes[f]
+    peak = lambda r: max(A[r], B[r])
+    for _ in range(4 * F):
+        hi = max(range(world), key=peak)
+        top = peak(hi)
+        best, best_pair = None, top
+        mine = [i for i in range(F) if owner[i] == hi]
+        for r in range(world):
+            if r == hi:
+                continue
+            theirs = [None] + [i for i in range(F) if owner[i] == r]
+            for f in mine:
+                for g in theirs:
+                    ga, gb, gt = (a[g], b[g], table_bytes[g]) if g is not None else (0.0, 0.0, 0)
+                    if used[r] + table_bytes[f] - gt > cap or used[hi] - table_bytes[f] + gt > cap:
+                        continue
+                    pair = max(A[hi] - a[f] + ga, B[hi] - b[f] + gb, A[r] + a[f] - ga, B[r] + b[f] - gb)
+                    if pair < best_pair - 1e-12:
+                        best, best_pair = (f, g, r), pair
+        if best is None:
+            break
+        f, g, r = best
+        owner[f] = r
+        A[hi] -= a[f]; B[hi] -= b[f]; used[hi] -= table_bytes[f]
+        A[r] += a[f]; B[r] += b[f]; used[r] += table_bytes[f]
+        if g is not None:
+            owner[g] = hi
+            A[r] -= a[g]; B[r] -= b[g]; used[r] -= table_bytes[g]
+            A[hi] += a[g]; B[hi] += b[g]; used[hi] += table_bytes[g]
+    return owner
+
+
+def shard_summary(owner: Sequence[int], table_bytes: Sequence[int], traffic: Sequence[float], world: int,
+                  exchange: Optional[Sequence[float]] = None) -> dict:
     load = [0.0] * world
     used = [0] * world
+    sent = [0.0] * world
     for f, r in enumerate(owner):
         load[r] += traffic[f]
         used[r] += table_bytes[f]
+        if exchange is not None:
+            sent[r] += exchange[f]
     mean = sum(load) / world if world else 0.0
-    return {"bytes_per_rank": used, "traffic_per_rank": load,
-            "traffic_imbalance": (max(load) / mean) if mean > 0 else 1.0}
+    out = {"bytes_per_rank": used, "traffic_per_rank": load,
+           "traffic_imbalance": (max(load) / mean) if mean > 0 else 1.0}
+    if exchange is not None:
+        mean_e = sum(sent) / world if world else 0.0
+        out["exchange_per_rank"] = sent
+        out["exchange_imbalance"] = (max(sent) / mean_e) if mean_e > 0 else 1.0
+    return out
 
 
 # ---------------------------------------------------------------------------
