@@ -70,6 +70,9 @@ def parse_args():
     p.add_argument("--compare-batch-order", action="store_true",
                    help="sharded path, peer exchange: also time the steps with tiles walked in batch order "
                         "(destination interleave off) and report that time beside the headline")
+    p.add_argument("--probe-exchange", action="store_true",
+                   help="sharded path, peer exchange: also time the steps on a batch of empty bags, i.e. the same "
+                        "stores to the same addresses with nothing gathered (the exchange alone)")
     p.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
                    help="sharded path: fused peer-memory stores, or pool + NCCL all-to-all + placement")
     return p.parse_args()
@@ -592,6 +595,21 @@ def run_sharded(args):
         if mod.local is not None:
             mod.local.set_peer_interleave(True)
 
+    t_probe = 0.0
+    if args.probe_exchange and args.exchange == "peer":
+        ev = [torch.zeros(1, dtype=torch.int32, device=dev) for _ in local]
+        eo = [torch.zeros(B + 1, dtype=torch.int32, device=dev) for _ in local]
+        for i in range(3):
+            run_step(ev, eo)
+        barrier()
+        ev6, ev7 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev6.record()
+        for i in range(K):
+            run_step(ev, eo)
+        ev7.record()
+        barrier()
+        t_probe = ev6.elapsed_time(ev7) * 1e-3
+
     t_e2e = None
     if not args.no_e2e:
         def e2e_step(i):
@@ -613,7 +631,7 @@ def run_sharded(args):
 
     launches_per_step = 1 if args.exchange == "peer" else args.chunks
     k_sum = sum(ktimes) / max(1, min(K, 256 // launches_per_step)) if ktimes else 0.0  # pooled-kernel ms per step, this rank
-    stats = torch.tensor([t_dev, t_e2e or 0.0, k_sum, float(sum(alg) / len(alg)), t_plain], dtype=torch.float64,
+    stats = torch.tensor([t_dev, t_e2e or 0.0, k_sum, float(sum(alg) / len(alg)), t_plain, t_probe], dtype=torch.float64,
                          device=dev)
     mx = stats.clone()
     dist.all_reduce(mx, op=dist.ReduceOp.MAX)
@@ -622,7 +640,7 @@ def run_sharded(args):
     if rank == 0:
         peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
         peak = float(json.load(open(peaks_path))["hbm_gbs"]) if os.path.exists(peaks_path) else 6650.0
-        t_dev, t_e2e_m, k_max, _, t_plain_m = [float(x) for x in mx]
+        t_dev, t_e2e_m, k_max, _, t_plain_m, t_probe_m = [float(x) for x in mx]
         total_alg = float(sm[3])
         h2d = sum(t.numel() * 4 for t in host[0][0]) + sum(t.numel() * 4 for t in host[0][1])
         exch = max(summ["exchange_per_rank"])  # bytes the busiest rank sends per step
@@ -656,6 +674,9 @@ def run_sharded(args):
         }
         if t_plain_m:
             line["config"]["batch_order_ms_per_step"] = t_plain_m / K * 1e3
+        if t_probe_m:
+            line["config"]["exchange_alone_ms_per_step"] = t_probe_m / K * 1e3
+            line["config"]["exchange_alone_gbs_per_rank"] = exch / (t_probe_m / K) / 1e9
         print(json.dumps(line), flush=True)
     dist.barrier()
     if args.exchange == "peer":

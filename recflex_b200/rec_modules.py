@@ -115,10 +115,14 @@ class FeatEmbed(nn.Module):
         self._staging_bytes = 0
 
     def __del__(self):
-        h = getattr(self, "_h", None)
-        if h is not None and h.value:
-            self._lib.eb_destroy(h)
-            self._h = C.c_void_p()
+        # may run while the interpreter shuts down, when nn.Module's attribute machinery is already gone
+        try:
+            h = self.__dict__.get("_h")
+            if h is not None and h.value:
+                self.__dict__["_h"] = None
+                self._lib.eb_destroy(h)
+        except Exception:
+            pass
 
     # -- schedules ---------------------------------------------------------
     @property
