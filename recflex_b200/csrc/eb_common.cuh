@@ -53,8 +53,8 @@ constexpr int kMaxPeers = 16;            // ranks whose output matrices one laun
 struct __align__(128) WsHeader {
   uint32_t ticket;        // next warp tile
   uint32_t total_tiles;
-  uint32_t cta_ticket;    // next tile of eb_warp_kernel (features on the warp-per-bag schedule)
-  uint32_t cta_tiles;     // its tile count
+  uint32_t cta_ticket;    // reserved (eb_warp_kernel runs a plain grid and draws no tickets); kept zero
+  uint32_t cta_tiles;     // CTAs of eb_warp_kernel that have work (features on the warp-per-bag schedule)
   uint32_t status;
   uint32_t pad_[27];
   float* peer_out[kMaxPeers];  // peer mode: output matrix of every rank (this GPU's view of their memory)

@@ -6,12 +6,15 @@
 // holds R = 32 / G row *slots*.  Accumulation is always fp32.
 //
 //   tile_group  (EB_SCHED_GROUP)  slot-per-bag, serial walk, no reduction
-//   tile_warp   (EB_SCHED_WARP)   warp-per-bag, slots split the bag, butterfly reduce
+//   tile_warp   (element-wise)    warp-per-bag for rows that are not a whole number of 16-byte lane loads
+//                                 (V = 1); EB_SCHED_WARP on vector rows is eb_warp_kernel (eb_warp.cuh)
 //   tile_flat   (EB_SCHED_FLAT)   flattened entry stream dealt round-robin to the slots,
 //                                 segmented reduce at bag boundaries
 //   tile_stream (EB_SCHED_STREAM) flattened entry stream cut into one contiguous piece per
 //                                 slot; each slot walks its piece serially, bags that
-//                                 straddle pieces are patched once per 32 bags
+//                                 straddle pieces are patched once per 32 bags; with D > 0
+//                                 (EB_SCHED_PIPE) the rows in flight sit in a cp.async ring in
+//                                 shared memory instead of registers
 //
 // They cover the same ground as the reference's ws:: / onehot:: / obms:: / rbk::
 // device templates (examples/csrc/include/*_kernel.cuh) but share one load/store
@@ -323,7 +326,8 @@ __device__ __forceinline__ void tile_group(const TileCtx& c, int64_t b0, int64_t
 }
 
 // ---------------------------------------------------------------------------
-// EB_SCHED_WARP: the warp owns one bag at a time; its R slots split the bag.
+// Warp-per-bag inside the fused kernel: the warp owns one bag at a time; its R slots
+// split the bag.  Used for the element-wise fallback only (V = 1).
 // ---------------------------------------------------------------------------
 template <typename T, int V, int U, bool IDX64>
 __device__ __forceinline__ void tile_warp(const TileCtx& c, int64_t b0, int64_t b1, int lane) {
