@@ -257,21 +257,27 @@ class Tuner:
                     global_ms[occ], winners[occ] = ms, uni
                 if kind != "warp" and ms < best_uni_ms:
                     best_uni, best_uni_ms = uni, ms
-            # long bags to the warp-per-bag kernel, everything else on the best uniform schedule of the fused kernel:
-            # the local stage ranks a feature's candidates inside ONE kernel and cannot see this split
-            for min_len in self.config.hybrid_min_len:
-                long_bags = [f for f in range(self.num_feats) if self.stats[f].mean_len >= min_len]
-                if best_uni is None or not long_bags or len(long_bags) == self.num_feats:
-                    continue
-                mix = list(best_uni)
-                for f in long_bags:
-                    mix[f] = Schedule("warp", 4)
+            for mix in self.hybrids(best_uni):
                 ms = self.fused_ms(mix, occ)
                 if ms < global_ms[occ]:
                     global_ms[occ], winners[occ] = ms, mix
         best = min(global_ms, key=global_ms.get)
         self.module.set_schedules(winners[best], occupancy=best)
         return TuneResult(winners[best], best, local, global_ms, self.stats)
+
+    def hybrids(self, base: Optional[Sequence[Schedule]]) -> List[List[Schedule]]:
+        """Assignments that send long bags to the warp-per-bag kernel and leave everything else as in `base`.  The
+        local stage ranks a feature's candidates inside ONE kernel and cannot see this split."""
+        out = []
+        for min_len in self.config.hybrid_min_len:
+            long_bags = [f for f in range(self.num_feats) if self.stats[f].mean_len >= min_len]
+            if base is None or not long_bags or len(long_bags) == self.num_feats:
+                continue
+            mix = list(base)
+            for f in long_bags:
+                mix[f] = Schedule("warp", 4)
+            out.append(mix)
+        return out
 
     def refine(self, result: TuneResult) -> TuneResult:
         """Greedy pass in the real fused kernel: for each cluster (heaviest first), try its best local candidates
@@ -372,11 +378,13 @@ class Tuner:
     def retune(self, result: TuneResult, new_batches) -> TuneResult:
         """Re-run the local stage only for features whose statistics moved bucket on `new_batches`, keep the
         occupancy sweep (distribution shift)."""
+        self.module.set_kernel_overlap(0)
         fresh = Tuner(self.module, new_batches, self.config)
         moved = set(needs_retune(result.stats, fresh.stats)) if result.stats else set(range(self.num_feats))
         if not moved:
             fresh.module.set_schedules(result.schedules, occupancy=result.occupancy)
-            return TuneResult(result.schedules, result.occupancy, {}, {}, fresh.stats)
+            fresh.module.set_kernel_overlap(result.overlap)
+            return TuneResult(result.schedules, result.occupancy, {}, {}, fresh.stats, result.overlap)
         local: Dict[int, Dict[int, List[float]]] = {}
         for members in fresh.clusters().values():
             todo = [f for f in members if f in moved]
@@ -395,9 +403,13 @@ class Tuner:
                 scheds[f] = fresh._cands[f][min(range(len(t)), key=t.__getitem__)]
             winners[occ] = scheds
             global_ms[occ] = fresh.fused_ms(scheds, occ)
+            for mix in fresh.hybrids(scheds):
+                ms = fresh.fused_ms(mix, occ)
+                if ms < global_ms[occ]:
+                    global_ms[occ], winners[occ] = ms, mix
         best = min(global_ms, key=global_ms.get)
         self.module.set_schedules(winners[best], occupancy=best)
-        return TuneResult(winners[best], best, local, global_ms, fresh.stats)
+        return fresh.tune_overlap(TuneResult(winners[best], best, local, global_ms, fresh.stats))
 
 
 def main(argv=None) -> None:
