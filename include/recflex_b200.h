@@ -39,6 +39,10 @@ extern "C" {
 /* table_dtype values */
 #define EB_F32 0
 #define EB_F16 1
+/* out_dtype values (eb_set_output_dtype): element type of the pooled output */
+#define EB_OUT_F32 0
+#define EB_OUT_BF16 1
+#define EB_OUT_F16 2
 /* index_dtype values (values and offsets share one dtype, as in torch.nn.EmbeddingBag) */
 #define EB_I32 0
 #define EB_I64 1
@@ -81,7 +85,9 @@ extern "C" {
  *                   registers; costs 64 KB of shared memory per CTA, so at most
  *                   3 CTAs per SM run (a higher occupancy setting is honoured
  *                   only up to what fits).  No counterpart in the reference.
- *   EB_SCHED_AUTO   let the library choose from dim, dtype and mean bag length.
+ *   EB_SCHED_AUTO   the library's default: EB_SCHED_STREAM with four rows in flight, whatever the feature
+ *                   looks like.  Choosing per feature from dim, dtype and bag lengths is the tuner's job
+ *                   (recflex_b200/tuning.py), which replaces this default.
  */
 #define EB_SCHED_AUTO 0
 #define EB_SCHED_GROUP 1
@@ -163,7 +169,8 @@ int eb_forward(eb_handle* h, int64_t batch, const void* const* values_ptrs,
 /*
  * Same, for one packed (jagged) batch: `values` holds all features' indices
  * back to back in feature order, `offsets` is a [num_features, batch+1] matrix
- * of per-feature offsets (each row starts at 0 and ends at nnz_f).  Both are
+ * of per-feature offsets (each row starts at 0 and ends at nnz_f; in eb_forward
+ * a feature's first offset may be any position of its index list).  Both are
  * DEVICE pointers; nothing is uploaded per call.
  * Replaces the packed d_arg_buffers / d_arg_buffer_offsets arguments of
  * FusedKnl (RecFlex/code_emitter/codegen.py:144-160, 318-331).
@@ -190,9 +197,12 @@ int eb_host_staging_bytes(const eb_handle* h, int64_t batch, int64_t total_nnz,
 /*
  * The fused forward with per-feature device time, the counterpart of
  * `timing=True` (RecFlex/code_emitter/codegen.py:301-316, 396-401;
- * RecFlex/rec_modules.py:96-109): each tile's globaltimer delta is summed per
- * feature.  per_feature_ns is a HOST array of num_features doubles; the call
- * synchronises `stream`.
+ * RecFlex/rec_modules.py:96-109): each tile's clock64() delta is summed per
+ * feature and converted to nanoseconds with the device's nominal (maximum) SM
+ * clock, as the reference converts its clock() deltas with cudaDevAttrClockRate.
+ * The figures rank a feature's schedules against each other; they are not
+ * absolute times whenever the SM clock runs below its maximum.  per_feature_ns
+ * is a HOST array of num_features doubles; the call synchronises `stream`.
  */
 int eb_forward_timed(eb_handle* h, int64_t batch, const void* const* values_ptrs,
                      const void* const* offsets_ptrs, const int64_t* nnz, int index_dtype,
@@ -258,6 +268,47 @@ int eb_forward_peers(eb_handle* h, int64_t batch, const void* const* values_ptrs
                      const void* const* offsets_ptrs, const int64_t* nnz, int index_dtype,
                      int offsets_have_end, float* const* peer_out, int world, int64_t out_ld,
                      void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Element type of the pooled output (no counterpart in the reference, whose
+ * output is hard-wired to fp32, RecFlex/code_emitter/codegen.py:416-421).
+ * EB_OUT_F32 is the default and the contract the parity tests pin.
+ * EB_OUT_BF16 / EB_OUT_F16 make every forward of this handle write its sums,
+ * still accumulated in fp32, rounded to nearest even into 2-byte elements:
+ * `out`, `out_ld` and the output buffers of the other entry points then count
+ * such elements (pass the buffer cast to float*).  Meant for consumers that
+ * cast anyway (the first linear layer of RecFlex/rec_modules.py:143-179's
+ * RecomModel in bf16): it halves the bytes written, downloaded and exchanged.
+ * A bag that the stream / pipe schedules cut in two has its first part rounded
+ * once more on the way; empty bags are exactly 0 in every type.
+ */
+int eb_set_output_dtype(eb_handle* h, int out_dtype);
+
+/*
+ * Pooling + exchange through the copy engines for table-wise sharding (no
+ * counterpart in the reference).  This rank pools ITS features for the whole
+ * batch into `send` ([batch, send_ld] elements of the output dtype, this GPU's
+ * memory) in ONE launch whose tile order walks the batch in `chunks` pieces:
+ * sample b belongs to destination rank b / (batch / world), and piece k holds
+ * rows [k, k + 1) * batch / (world * chunks) of every destination.  As soon as
+ * the kernel has finished a piece (a device flag the kernel raises; the copy
+ * stream waits for it with a stream memory operation, the host is not
+ * involved), `copy_stream` copies the piece's rows to every destination:
+ * rank d receives them in peer_out[d] ([batch / world, out_ld] elements, THIS
+ * process's pointer to rank d's matrix, see eb_peer_open) at columns
+ * [out_col, out_col + output units), rows in batch order.  The copies of piece
+ * k run while piece k + 1 is pooled.  A kernel launched right after the
+ * pooling kernel raises every flag, so the copy stream can never wait longer
+ * than the pooling runs.  The caller orders consumers after all ranks' copy
+ * streams, and must not reuse `send` before `copy_stream` is done with it.
+ * batch must be a multiple of world * chunks; world <= 16, chunks <= 64.
+ * Returns EB_ERR_UNSUPPORTED when the driver has no stream memory operations.
+ */
+int eb_forward_exchange(eb_handle* h, int64_t batch, const void* const* values_ptrs,
+                        const void* const* offsets_ptrs, const int64_t* nnz, int index_dtype,
+                        int offsets_have_end, float* send, int64_t send_ld, float* const* peer_out,
+                        int world, int rank, int64_t out_ld, int64_t out_col, int chunks,
+                        void* workspace, size_t workspace_bytes, void* stream, void* copy_stream);
 
 /*
  * Overlap of the two pooling kernels (no counterpart in the reference, whose
@@ -351,17 +402,26 @@ int eb_parse_bags(const char* text, size_t text_len, int64_t batch, int32_t* val
  * All calls on a GPU share that array and it keeps the previous call's
  * contents; each call rewrites the descriptors and its binding kernel resets
  * the counters and the status word, so back-to-back calls on one stream are
- * safe, while calls that overlap on the GPU (other streams, other host
- * threads) race.  The host-side staging of the descriptors is a single static
- * buffer too: do not call this from two host threads at once.  The first call
- * on each device resolves the array's device address (cudaGetSymbolAddress);
- * make that first call before any stream capture begins.
+ * safe, while calls whose kernels overlap on the GPU (other streams) race.
+ * On the host, calls for one GPU are serialised by a lock and every GPU has
+ * its own staging buffer, so threads driving different GPUs do not interfere.
+ * The first call on each device resolves the array's device address
+ * (cudaGetSymbolAddress); make that first call before any stream capture
+ * begins.  Every call stages its descriptors through host memory that the next
+ * call overwrites, so a call is refused (EB_ERR_UNSUPPORTED) while its stream
+ * is being captured.  At most 16 devices per process.
+ *
+ * eb_noalloc_check_status reads the status word of the last call on `device`
+ * out of the built-in array (the role eb_check_status plays for a handle's
+ * workspace): EB_ERR_BAD_INPUT when that call met an index outside [0, rows)
+ * or offsets that had to be clamped.  Synchronises `stream`; allocates nothing.
  */
 #define EB_NOALLOC_MAX_FEATURES 1024
 int eb_forward_packed_noalloc(int device, int num_features, const int64_t* rows, const int32_t* dims,
                               const int32_t* table_dtype, const void* const* table_ptrs, int64_t batch,
                               const void* values, const void* offsets, int index_dtype, float* out,
                               int64_t out_ld, void* stream);
+int eb_noalloc_check_status(int device, void* stream);
 
 /* Message of the calling thread's last failure ("" if none). */
 const char* eb_last_error(void);

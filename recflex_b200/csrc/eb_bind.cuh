@@ -64,11 +64,13 @@ __global__ void __launch_bounds__(kBindThreads) eb_bind_kernel(LaunchArgs a, int
   const int64_t B = a.batch;
   uint32_t status = 0;
 
-  // pass 1: index counts, packed-mode pointers, gathered bytes of the batch
+  // pass 1: index counts, packed-mode pointers, gathered bytes of the batch.  The first boundary need not be 0
+  // (a caller may pass a window of a longer offsets array): the work estimate counts the indices between the
+  // first and the last boundary, while clamping uses the absolute end.
   long long carry = 0, my_bytes = 0;
   for (int base = 0; base < F; base += kBindThreads) {
     const int f = base + tid;
-    long long nnz = 0;
+    long long nnz = 0, work = 0;
     const char* offp = nullptr;
     if (f < F) {
       if (a.packed) {
@@ -80,8 +82,12 @@ __global__ void __launch_bounds__(kBindThreads) eb_bind_kernel(LaunchArgs a, int
         nnz = a.has_end ? load_index(d.offsets, B, a.idx64) : d.nnz;
       }
       if (nnz < 0) { nnz = 0; status |= kStatusBadOffsets; }
+      long long first = (B > 0 || a.has_end) ? load_index(offp, 0, a.idx64) : 0;
+      first = first < 0 ? 0 : (first > nnz ? nnz : first);
+      work = nnz - first;
     }
     long long total;
+    // packed mode: a feature's indices start where the previous feature's end (rows of the offsets matrix start at 0)
     const long long excl = block_excl_scan(nnz, s_warp, total) + carry;
     carry += total;
     if (f < F) {
@@ -90,7 +96,8 @@ __global__ void __launch_bounds__(kBindThreads) eb_bind_kernel(LaunchArgs a, int
         dyn[f].offsets = offp;
       }
       dyn[f].nnz = nnz;
-      my_bytes += nnz * (long long)a.feats[f].row_bytes;
+      dyn[f].work = work;
+      my_bytes += work * (long long)a.feats[f].row_bytes;
       if (zero_ns) feat_ns[f] = 0ull;
     }
   }
@@ -99,15 +106,18 @@ __global__ void __launch_bounds__(kBindThreads) eb_bind_kernel(LaunchArgs a, int
 
   // pass 2: bags per tile.  Tiles aim at the same gathered bytes so that a
   // ticket costs about the same whatever the feature; about 16 tiles per warp.
+  // In chunked order a tile must stay inside one piece of chunk_rows bags.
+  const long long piece_cap = a.chunks > 0 ? (a.chunk_rows & -a.chunk_rows) : (1ll << 30);
   long long target = total_bytes / ((long long)a.warps_total * 16);
   target = target < (16 << 10) ? (16 << 10) : (target > (256 << 10) ? (256 << 10) : target);
   for (int f = tid; f < F; f += kBindThreads) {
     const FeatStatic fs = a.feats[f];
-    long long mean_bytes = B > 0 ? dyn[f].nnz * (long long)fs.row_bytes / B : 0;
+    long long mean_bytes = B > 0 ? dyn[f].work * (long long)fs.row_bytes / B : 0;
     if (mean_bytes < fs.row_bytes) mean_bytes = fs.row_bytes;
     int n = fs.bags_per_tile > 0 ? fs.bags_per_tile : pow2_floor(target / mean_bytes);
     const int lo = fs.bags_per_tile > 0 ? 1 : (fs.kind == 1 /*GROUP*/ ? 32 : 1);
     n = n < lo ? lo : (n > 1024 ? 1024 : n);
+    if (n > piece_cap) n = (int)piece_cap;
     bpt[f] = n;
     if (F <= kMaxLptFeatures) s_cost[f] = (float)n * (float)mean_bytes;
   }
@@ -129,8 +139,10 @@ __global__ void __launch_bounds__(kBindThreads) eb_bind_kernel(LaunchArgs a, int
   __syncthreads();
 
   // pass 4: exclusive prefix sums of tile counts in that order, one per kernel: features on the warp-per-bag
-  // schedule (kind 2, vector path) are pooled by eb_warp_kernel, all others by eb_fused_kernel
+  // schedule (kind 2, vector path) are pooled by eb_warp_kernel, all others by eb_fused_kernel.  In chunked
+  // order the fused kernel's prefix sum covers ONE chunk (batch / chunks bags); its tickets repeat it per chunk.
   int32_t* warp_prefix = reinterpret_cast<int32_t*>(a.ws + L.cta_prefix);
+  const int64_t tile_bags = a.chunks > 0 ? B / a.chunks : B;
   carry = 0;
   long long carry_w = 0;
   for (int base = 0; base < F; base += kBindThreads) {
@@ -139,7 +151,7 @@ __global__ void __launch_bounds__(kBindThreads) eb_bind_kernel(LaunchArgs a, int
     if (k < F) {
       const int f = order[k];
       const bool lean = a.feats[f].kind == 2 && a.feats[f].vec != 0;
-      t = lean ? 0 : tiles_of(B, bpt[f]);
+      t = lean ? 0 : tiles_of(tile_bags, bpt[f]);
       tw = lean ? (B + kWarpsPerCta - 1) / kWarpsPerCta : 0;  // eb_warp_kernel: one CTA per 8 bags
     }
     long long total;
@@ -157,12 +169,20 @@ __global__ void __launch_bounds__(kBindThreads) eb_bind_kernel(LaunchArgs a, int
     tile_prefix[F] = (int32_t)carry;
     warp_prefix[F] = (int32_t)carry_w;
     hdr->ticket = 0;
-    hdr->total_tiles = (uint32_t)carry;
+    hdr->total_tiles = (uint32_t)(carry * (a.chunks > 0 ? a.chunks : 1));
     hdr->cta_ticket = 0;
     hdr->cta_tiles = (uint32_t)carry_w;
     hdr->status = status;
   }
   if (tid < kMaxPeers) hdr->peer_out[tid] = a.peer_out[tid];
+  if (tid < kMaxChunks) reinterpret_cast<ChunkSync*>(a.ws + L.chunk_sync)->done[tid] = 0u;
+}
+
+// Sets every chunk flag to the call's epoch.  Launched right after the fused kernel in chunked order, so that a
+// stream waiting for a flag can never wait longer than that kernel runs, whatever the counts did.
+__global__ void eb_release_kernel(uint32_t* flags, int n, uint32_t epoch) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) *reinterpret_cast<volatile uint32_t*>(flags + i) = epoch;
 }
 
 // ---------------------------------------------------------------------------

@@ -93,6 +93,8 @@ struct eb_handle {
   bool time_kernels = false;
   std::vector<cudaEvent_t> t0, t1;
   int t_count = 0;
+  int out_dtype = EB_OUT_F32;  // element type of the output matrix
+  uint32_t epoch = 0;          // calls in chunked ticket order so far (eb_forward_exchange)
 };
 
 namespace {
@@ -131,6 +133,16 @@ int upload_feats(eb_handle* h) {
   return EB_OK;
 }
 
+size_t out_elem_bytes(const eb_handle* h) { return h->out_dtype == EB_OUT_F32 ? 4 : 2; }
+
+// Widest aligned store the output allows: 2 = eight elements, 1 = four, 0 = one (see store_vals).
+int out_vec_of(const void* out, int64_t out_ld, size_t es) {
+  const uintptr_t p = reinterpret_cast<uintptr_t>(out);
+  if (p % (8 * es) == 0 && out_ld % 8 == 0) return 2;
+  if (p % (4 * es) == 0 && out_ld % 4 == 0) return 1;
+  return 0;
+}
+
 int check_forward_common(const eb_handle* h, int64_t batch, int index_dtype, const float* out, int64_t out_ld,
                          const void* workspace, size_t workspace_bytes) {
   if (!h) return fail(EB_ERR_INVALID_ARG, "null handle");
@@ -139,7 +151,9 @@ int check_forward_common(const eb_handle* h, int64_t batch, int index_dtype, con
     return fail(EB_ERR_INVALID_ARG, "index_dtype must be EB_I32 or EB_I64 (got %d)", index_dtype);
   if (batch > 0 && !out) return fail(EB_ERR_INVALID_ARG, "null output pointer");
   if (out_ld < h->units) return fail(EB_ERR_INVALID_ARG, "out_ld %lld < output units %lld", (long long)out_ld, (long long)h->units);
-  if ((reinterpret_cast<uintptr_t>(out) & 3) != 0) return fail(EB_ERR_INVALID_ARG, "output pointer is not 4-byte aligned");
+  if (out_ld >= (1ll << 30)) return fail(EB_ERR_TOO_LARGE, "out_ld %lld: output rows must stay below 2^30 elements", (long long)out_ld);
+  if ((reinterpret_cast<uintptr_t>(out) & (out_elem_bytes(h) - 1)) != 0)
+    return fail(EB_ERR_INVALID_ARG, "output pointer is not aligned to its element size");
   if (!workspace) return fail(EB_ERR_INVALID_ARG, "null workspace");
   if ((reinterpret_cast<uintptr_t>(workspace) & 127) != 0) return fail(EB_ERR_INVALID_ARG, "workspace must be 128-byte aligned");
   const size_t need = ws_layout(h->num_features).total;
@@ -163,9 +177,8 @@ LaunchArgs make_args(const eb_handle* h, int64_t batch, int index_dtype, int has
   a.idx64 = index_dtype == EB_I64;
   a.has_end = has_end != 0;
   a.packed = 0;
-  a.out_vec = ((reinterpret_cast<uintptr_t>(out) & 31) == 0 && out_ld % 8 == 0)
-                  ? 2
-                  : (((reinterpret_cast<uintptr_t>(out) & 15) == 0 && out_ld % 4 == 0) ? 1 : 0);
+  a.out_dtype = h->out_dtype;
+  a.out_vec = out_vec_of(out, out_ld, out_elem_bytes(h));
   a.warps_total = h->sm_count * h->occupancy * kWarpsPerCta;
   a.ring_bytes = (int32_t)(h->smem_bytes / kWarpsPerCta);
   return a;
@@ -179,7 +192,8 @@ int run(eb_handle* h, const LaunchArgs& a_in, bool timing, cudaStream_t st) {
   // reduced grid (it holds its CTA slots until its tickets run out); eb_warp_kernel's plain grid fills the rest of
   // every SM from a second stream, forked after the binding kernel and joined before anything the caller enqueues
   // next.  The per-feature timing variant keeps the serial order.
-  const bool overlap = h->overlap_ctas > 0 && h->warp_features > 0 && h->warp_features < h->num_features && !timing;
+  const bool overlap = h->overlap_ctas > 0 && h->warp_features > 0 && h->warp_features < h->num_features && !timing &&
+                       a.chunks == 0;  // chunked order: the warp-per-bag kernel must be done before any chunk is published
   const int ctas_per_sm = overlap && h->overlap_ctas < h->occupancy ? h->overlap_ctas : h->occupancy;
   a.warps_total = h->sm_count * ctas_per_sm * kWarpsPerCta;
   EB_CUDA(launch_bind(a, timing, st));
@@ -196,6 +210,7 @@ int run(eb_handle* h, const LaunchArgs& a_in, bool timing, cudaStream_t st) {
     if (h->warp_features) EB_CUDA(launch_warp(a, timing, h->warp_features, st));
     EB_CUDA(launch_fused(a, h->occupancy, timing, h->sm_count * ctas_per_sm, h->smem_bytes, st));
   }
+  if (a.chunks > 0) EB_CUDA(launch_release(a, st));
   if (rec) {
     EB_CUDA(cudaEventRecord(h->t1[h->t_count], st));
     ++h->t_count;
@@ -216,7 +231,7 @@ int upload_dyn(eb_handle* h, int64_t batch, const void* const* values_ptrs, cons
     p[f].values = static_cast<const char*>(values_ptrs[f]);
     p[f].offsets = static_cast<const char*>(offsets_ptrs[f]);
     p[f].nnz = has_end ? 0 : nnz[f];
-    p[f].pad_ = 0;
+    p[f].work = 0;
     if (!offsets_ptrs[f] && batch > 0) return fail(EB_ERR_INVALID_ARG, "feature %d: null offsets pointer", f);
     if (!has_end && nnz[f] < 0) return fail(EB_ERR_INVALID_ARG, "feature %d: negative nnz", f);
   }
@@ -436,13 +451,13 @@ int eb_forward_peers(eb_handle* h, int64_t batch, const void* const* values_ptrs
   if (batch % world != 0 || (batch / world) % 32 != 0)
     return fail(EB_ERR_INVALID_ARG, "batch / world must be a whole multiple of 32 (batch %lld, world %d)",
                 (long long)batch, world);
-  int vec = out_ld % 8 == 0 ? 2 : (out_ld % 4 == 0 ? 1 : 0);
+  int vec = 2;
   for (int r = 0; r < world; ++r) {
     if (!peer_out[r]) return fail(EB_ERR_INVALID_ARG, "null output pointer for rank %d", r);
-    const uintptr_t p = reinterpret_cast<uintptr_t>(peer_out[r]);
-    if (p & 3) return fail(EB_ERR_INVALID_ARG, "rank %d: output not 4-byte aligned", r);
-    if (vec == 2 && (p & 31)) vec = 1;
-    if (vec == 1 && (p & 15)) vec = 0;
+    if (reinterpret_cast<uintptr_t>(peer_out[r]) & (out_elem_bytes(h) - 1))
+      return fail(EB_ERR_INVALID_ARG, "rank %d: output not aligned to its element size", r);
+    const int v = out_vec_of(peer_out[r], out_ld, out_elem_bytes(h));
+    vec = v < vec ? v : vec;
   }
   DeviceGuard guard(h->device);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -454,6 +469,80 @@ int eb_forward_peers(eb_handle* h, int64_t batch, const void* const* values_ptrs
   a.peer_spread = h->peer_interleave ? world : 0;
   for (int r = 0; r < world; ++r) a.peer_out[r] = peer_out[r];
   return run(h, a, false, st);
+}
+
+int eb_set_output_dtype(eb_handle* h, int out_dtype) {
+  if (!h) return fail(EB_ERR_INVALID_ARG, "null handle");
+  if (out_dtype != EB_OUT_F32 && out_dtype != EB_OUT_BF16 && out_dtype != EB_OUT_F16)
+    return fail(EB_ERR_INVALID_ARG, "out_dtype must be EB_OUT_F32, EB_OUT_BF16 or EB_OUT_F16 (got %d)", out_dtype);
+  h->out_dtype = out_dtype;
+  return EB_OK;
+}
+
+namespace {
+// cuStreamWaitValue32 of the driver API, looked up at run time so that the library links against the runtime only.
+typedef int (*StreamWaitValue32)(cudaStream_t, unsigned long long, uint32_t, unsigned int);
+StreamWaitValue32 stream_wait_value32() {
+  static StreamWaitValue32 fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+    if (cudaGetDriverEntryPoint("cuStreamWaitValue32", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<StreamWaitValue32>(p);
+  }();
+  return fn;
+}
+}  // namespace
+
+int eb_forward_exchange(eb_handle* h, int64_t batch, const void* const* values_ptrs, const void* const* offsets_ptrs,
+                        const int64_t* nnz, int index_dtype, int offsets_have_end, float* send, int64_t send_ld,
+                        float* const* peer_out, int world, int rank, int64_t out_ld, int64_t out_col, int chunks,
+                        void* workspace, size_t workspace_bytes, void* stream, void* copy_stream) {
+  if (world < 1 || world > kMaxPeers) return fail(EB_ERR_INVALID_ARG, "world must be 1..%d (got %d)", kMaxPeers, world);
+  if (rank < 0 || rank >= world) return fail(EB_ERR_INVALID_ARG, "rank %d outside [0, %d)", rank, world);
+  if (chunks < 1 || chunks > kMaxChunks) return fail(EB_ERR_INVALID_ARG, "chunks must be 1..%d (got %d)", kMaxChunks, chunks);
+  if (!peer_out) return fail(EB_ERR_INVALID_ARG, "null peer_out");
+  int rc = check_forward_common(h, batch, index_dtype, send, send_ld, workspace, workspace_bytes);
+  if (rc != EB_OK) return rc;
+  if (batch == 0) return EB_OK;
+  if (batch % ((int64_t)world * chunks) != 0)
+    return fail(EB_ERR_INVALID_ARG, "batch %lld must be a whole multiple of world * chunks = %d", (long long)batch, world * chunks);
+  if (out_col < 0 || out_col + h->units > out_ld || out_ld >= (1ll << 30))
+    return fail(EB_ERR_INVALID_ARG, "columns [%lld, %lld) do not fit rows of %lld elements", (long long)out_col,
+                (long long)(out_col + h->units), (long long)out_ld);
+  for (int r = 0; r < world; ++r)
+    if (!peer_out[r]) return fail(EB_ERR_INVALID_ARG, "null output pointer for rank %d", r);
+  StreamWaitValue32 wait32 = stream_wait_value32();
+  if (!wait32) return fail(EB_ERR_UNSUPPORTED, "the driver offers no cuStreamWaitValue32 (stream memory operations)");
+  DeviceGuard guard(h->device);
+  cudaStream_t st = static_cast<cudaStream_t>(stream), cst = static_cast<cudaStream_t>(copy_stream);
+  rc = upload_dyn(h, batch, values_ptrs, offsets_ptrs, nnz, offsets_have_end, workspace, st);
+  if (rc != EB_OK) return rc;
+  LaunchArgs a = make_args(h, batch, index_dtype, offsets_have_end, send, send_ld, workspace);
+  a.chunks = chunks;
+  a.dest_rows = batch / world;
+  a.chunk_rows = a.dest_rows / chunks;
+  if (++h->epoch == 0) h->epoch = 1;  // a fresh workspace holds zeros: epoch 0 is never waited for
+  a.epoch = h->epoch;
+  rc = run(h, a, false, st);
+  if (rc != EB_OK) return rc;
+  // copy stream: as soon as chunk k is published, its rows leave for every destination
+  const size_t es = out_elem_bytes(h);
+  const ChunkSync* cs = reinterpret_cast<const ChunkSync*>(static_cast<char*>(workspace) + ws_layout(h->num_features).chunk_sync);
+  const size_t width = (size_t)h->units * es;
+  for (int k = 0; k < chunks; ++k) {
+    const int wrc = wait32(cst, (unsigned long long)reinterpret_cast<uintptr_t>(&cs->flag[k]), a.epoch, 0u /* >= */);
+    if (wrc != 0) return fail(EB_ERR_CUDA, "cuStreamWaitValue32 failed with driver error %d", wrc);
+    for (int i = 1; i <= world; ++i) {
+      const int d = (rank + i) % world;  // every rank starts with its right-hand neighbour; its own rows go last
+      const char* src = reinterpret_cast<const char*>(send) + ((size_t)d * a.dest_rows + (size_t)k * a.chunk_rows) * send_ld * es;
+      char* dst = reinterpret_cast<char*>(peer_out[d]) + ((size_t)k * a.chunk_rows * out_ld + out_col) * es;
+      EB_CUDA(cudaMemcpy2DAsync(dst, (size_t)out_ld * es, src, (size_t)send_ld * es, width, (size_t)a.chunk_rows,
+                                cudaMemcpyDefault, cst));
+    }
+  }
+  return EB_OK;
 }
 
 int eb_set_kernel_overlap(eb_handle* h, int fused_ctas_per_sm) {
@@ -538,7 +627,7 @@ int eb_host_staging_bytes(const eb_handle* h, int64_t batch, int64_t total_nnz, 
   const size_t isz = index_dtype == EB_I64 ? 8 : 4;
   size_t o = align_up((size_t)total_nnz * isz, 256);
   o = align_up(o + (size_t)h->num_features * (size_t)(batch + 1) * isz, 256);
-  o = align_up(o + (size_t)batch * (size_t)h->units * sizeof(float), 256);
+  o = align_up(o + (size_t)batch * (size_t)h->units * out_elem_bytes(h), 256);
   *bytes = o;
   return EB_OK;
 }
@@ -566,7 +655,7 @@ int eb_forward_host(eb_handle* h, int64_t batch, const void* host_values, int64_
   EB_CUDA(cudaMemcpyAsync(d_offsets, host_offsets, off_bytes, cudaMemcpyHostToDevice, st));
   rc = eb_forward_packed(h, batch, d_values, d_offsets, index_dtype, d_out, h->units, workspace, workspace_bytes, stream);
   if (rc != EB_OK) return rc;
-  EB_CUDA(cudaMemcpyAsync(host_out, d_out, (size_t)batch * (size_t)h->units * sizeof(float), cudaMemcpyDeviceToHost, st));
+  EB_CUDA(cudaMemcpyAsync(host_out, d_out, (size_t)batch * (size_t)h->units * out_elem_bytes(h), cudaMemcpyDeviceToHost, st));
   return EB_OK;
 }
 

@@ -42,8 +42,8 @@ static_assert(sizeof(FeatStatic) == 64, "FeatStatic must stay 64 bytes");
 struct __align__(8) FeatDyn {
   const char* values;
   const char* offsets;
-  int64_t nnz;
-  int64_t pad_;
+  int64_t nnz;      // end of the feature's index list (the last boundary; offsets are clamped to [0, nnz])
+  int64_t work;     // indices this call pools: nnz minus the first boundary (written by the binding kernel)
 };
 static_assert(sizeof(FeatDyn) == 32, "FeatDyn must stay 32 bytes");
 
@@ -61,15 +61,26 @@ struct __align__(128) WsHeader {
 };
 static_assert(sizeof(WsHeader) == 256, "WsHeader must stay 256 bytes");
 
+constexpr int kMaxChunks = 64;           // batch chunks of the chunked ticket order
+
+// Chunked order: done[k] counts the finished tiles of chunk k (zeroed by the binding kernel of every call);
+// flag[k] receives the call's epoch when the chunk's last tile is done.  Epochs only grow, so the flags are never
+// reset and a waiter compares with "at least this call's epoch".
+struct __align__(128) ChunkSync {
+  uint32_t done[kMaxChunks];
+  uint32_t flag[kMaxChunks];
+};
+static_assert(sizeof(ChunkSync) == 512, "ChunkSync must stay 512 bytes");
+
 // Host/device view of where each array sits inside the workspace.
 struct WsLayout {
-  size_t header, tile_prefix, cta_prefix, order, bags_per_tile, dyn, feat_ns, total;
+  size_t header, tile_prefix, cta_prefix, order, bags_per_tile, dyn, feat_ns, chunk_sync, total;
 };
 
-__host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+__host__ __device__ constexpr inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
-__host__ __device__ inline WsLayout ws_layout(int F) {
-  WsLayout l;
+__host__ __device__ constexpr inline WsLayout ws_layout(int F) {
+  WsLayout l{};
   size_t o = 0;
   l.header = o;        o += sizeof(WsHeader);
   l.tile_prefix = o;   o = align_up(o + sizeof(int32_t) * (size_t)(F + 1), 128);
@@ -78,6 +89,7 @@ __host__ __device__ inline WsLayout ws_layout(int F) {
   l.bags_per_tile = o; o = align_up(o + sizeof(int32_t) * (size_t)F, 128);
   l.dyn = o;           o = align_up(o + sizeof(FeatDyn) * (size_t)F, 128);
   l.feat_ns = o;       o = align_up(o + sizeof(unsigned long long) * (size_t)F, 128);
+  l.chunk_sync = o;    o += sizeof(ChunkSync);
   l.total = o;
   return l;
 }
@@ -95,10 +107,19 @@ struct LaunchArgs {
   int32_t idx64;          // values/offsets are int64 (else int32)
   int32_t has_end;        // offsets carry batch + 1 entries
   int32_t packed;
-  int32_t out_vec;        // out base and out_ld allow 16-byte (1) or 32-byte (2) stores
+  int32_t out_vec;        // out base and out_ld allow stores of four (1) or eight (2) aligned elements
+  int32_t out_dtype;      // output element type: 0 = fp32, 1 = bfloat16, 2 = binary16 (out_ld counts elements)
   int32_t warps_total;    // persistent warps of the fused kernel (for tile sizing)
   int32_t ring_bytes;     // shared memory per warp for the pipelined schedule's ring (0 when no feature uses it)
   int32_t peer_spread;    // peer mode: number of ranks to deal a feature's consecutive tiles over (0 = batch order)
+  // chunked ticket order (chunks > 0; for exchanges that ship finished chunks while later ones are pooled): the
+  // batch is seen as `world` runs of dest_rows bags (one per destination rank), each cut into `chunks` pieces of
+  // chunk_rows bags; the tickets cover piece 0 of every run for every feature, then piece 1, ...  A tile never
+  // straddles two pieces (the binding kernel makes bags_per_tile divide chunk_rows).
+  int32_t chunks;
+  uint32_t epoch;         // value written to a chunk's flag when its last tile is done
+  int64_t chunk_rows;
+  int64_t dest_rows;
   // peer mode (rows_per_peer > 0): sample b is stored to peer_out[b / rows_per_peer], row b % rows_per_peer
   int64_t rows_per_peer;
   float* peer_out[kMaxPeers];

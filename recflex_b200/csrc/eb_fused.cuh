@@ -28,14 +28,30 @@ namespace ebk {
     EB_DISPATCH_UNROLL(FN, float, 4, I64)                          \
   }
 
+// EB_SCHED_STREAM: the register walk
+#define EB_DISPATCH_STREAM_T(T, V, I64)                                        \
+  switch (fs.unroll) {                                                         \
+    case 1: tile_stream<T, V, 1, I64>(ctx, b0, b1, lane, items); break;        \
+    case 2: tile_stream<T, V, 2, I64>(ctx, b0, b1, lane, items); break;        \
+    case 4: tile_stream<T, V, 4, I64>(ctx, b0, b1, lane, items); break;        \
+    default: tile_stream<T, V, 8, I64>(ctx, b0, b1, lane, items); break;       \
+  }
+
+#define EB_DISPATCH_STREAM(I64)                                    \
+  if (fs.dtype == 1) {                                             \
+    EB_DISPATCH_STREAM_T(__half, 8, I64)                           \
+  } else {                                                         \
+    EB_DISPATCH_STREAM_T(float, 4, I64)                            \
+  }
+
 // EB_SCHED_PIPE: ring depth is tied to the unroll so that a CTA needs 32 to 64 KB
 // of shared memory: unroll 2 -> 4 stages, 4 -> 3 stages, 8 -> 2 stages.
 #define EB_DISPATCH_PIPE_T(T, V, I64)                                                  \
   switch (fs.unroll) {                                                                 \
     case 1:                                                                            \
-    case 2: tile_stream<T, V, 2, I64, 4>(ctx, b0, b1, lane, ring); break;              \
-    case 4: tile_stream<T, V, 4, I64, 3>(ctx, b0, b1, lane, ring); break;              \
-    default: tile_stream<T, V, 8, I64, 2>(ctx, b0, b1, lane, ring); break;             \
+    case 2: tile_stream<T, V, 2, I64, 4>(ctx, b0, b1, lane, items, ring); break;       \
+    case 4: tile_stream<T, V, 4, I64, 3>(ctx, b0, b1, lane, items, ring); break;       \
+    default: tile_stream<T, V, 8, I64, 2>(ctx, b0, b1, lane, items, ring); break;      \
   }
 
 #define EB_DISPATCH_PIPE(I64)                                      \
@@ -60,10 +76,11 @@ namespace ebk {
   } else if (fs.kind == 3) {                                       \
     EB_DISPATCH_DTYPE_U4(tile_flat, true)                          \
   } else if (fs.kind == 4) {                                       \
-    EB_DISPATCH_DTYPE_U4(tile_stream, true)                        \
+    if (fs.dtype == 1) tile_stream<__half, 8, 4, true>(ctx, b0, b1, lane, items); \
+    else tile_stream<float, 4, 4, true>(ctx, b0, b1, lane, items); \
   } else {                                                         \
-    if (fs.dtype == 1) tile_stream<__half, 8, 4, true, 3>(ctx, b0, b1, lane, ring); \
-    else tile_stream<float, 4, 4, true, 3>(ctx, b0, b1, lane, ring); \
+    if (fs.dtype == 1) tile_stream<__half, 8, 4, true, 3>(ctx, b0, b1, lane, items, ring); \
+    else tile_stream<float, 4, 4, true, 3>(ctx, b0, b1, lane, items, ring); \
   }
 
 #define EB_DISPATCH_KIND(I64)                                      \
@@ -75,7 +92,7 @@ namespace ebk {
   } else if (fs.kind == 3) {                                       \
     EB_DISPATCH_DTYPE(tile_flat, I64)                              \
   } else if (fs.kind == 4) {                                       \
-    EB_DISPATCH_DTYPE(tile_stream, I64)                            \
+    EB_DISPATCH_STREAM(I64)                                        \
   } else {                                                         \
     EB_DISPATCH_PIPE(I64)                                          \
   }
@@ -92,9 +109,15 @@ __global__ void __launch_bounds__(kCtaThreads, OCC) eb_fused_kernel(LaunchArgs a
   const FeatDyn* dyn = reinterpret_cast<const FeatDyn*>(a.ws + L.dyn);
   unsigned long long* feat_ns = reinterpret_cast<unsigned long long*>(a.ws + L.feat_ns);
   const uint32_t total = hdr->total_tiles;
+  // chunked order (a.chunks > 0): the tickets walk the batch chunk by chunk, every feature's tiles of chunk 0
+  // first, and the warp that completes a chunk's last tile publishes the chunk (see LaunchArgs)
+  const uint32_t per_chunk = a.chunks > 0 ? (uint32_t)__ldg(tile_prefix + F) : total;
   // per-warp ring of the pipelined schedule (a.ring_bytes per warp when any feature uses it, else none)
   extern __shared__ __align__(16) unsigned char eb_smem[];
   unsigned char* ring = eb_smem + (threadIdx.x >> 5) * a.ring_bytes;
+  // per-warp list of a chunk's non-empty bags (stream and pipe schedules)
+  __shared__ int2 eb_items[kWarpsPerCta][kBagItems];
+  int2* items = eb_items[threadIdx.x >> 5];
 
   uint32_t t = 0;
   if (lane == 0) t = atomicAdd(&hdr->ticket, 1u);
@@ -104,18 +127,29 @@ __global__ void __launch_bounds__(kCtaThreads, OCC) eb_fused_kernel(LaunchArgs a
     uint32_t tn = 0;
     if (lane == 0) tn = atomicAdd(&hdr->ticket, 1u);
 
-    int lo = 0, hi = F;  // tile_prefix[lo] <= t < tile_prefix[hi]
+    uint32_t chunk = 0, tt = t;
+    if (a.chunks > 0) {
+      chunk = t / per_chunk;
+      tt = t - chunk * per_chunk;
+    }
+    int lo = 0, hi = F;  // tile_prefix[lo] <= tt < tile_prefix[hi]
     while (hi - lo > 1) {
       const int mid = (lo + hi) >> 1;
-      if ((uint32_t)__ldg(tile_prefix + mid) <= t) lo = mid; else hi = mid;
+      if ((uint32_t)__ldg(tile_prefix + mid) <= tt) lo = mid; else hi = mid;
     }
     const int f = __ldg(order + lo);
-    int64_t tile = (int64_t)(t - (uint32_t)__ldg(tile_prefix + lo));
+    int64_t tile = (int64_t)(tt - (uint32_t)__ldg(tile_prefix + lo));
     const FeatStatic fs = a.feats[f];
     const FeatDyn fd = dyn[f];
     const int n = __ldg(bpt + f);
     if (a.peer_spread) tile = spread_tile(tile, n, a.peer_spread, a.rows_per_peer);
-    const int64_t b0 = tile * n;
+    int64_t b0 = tile * n;
+    if (a.chunks > 0) {
+      // tile of the chunk's own bag numbering [0, world * chunk_rows): destination d's run of chunk_rows bags
+      // starts at batch position d * dest_rows + chunk * chunk_rows; n divides chunk_rows
+      const int64_t d = b0 / a.chunk_rows;
+      b0 = d * a.dest_rows + (int64_t)chunk * a.chunk_rows + (b0 - d * a.chunk_rows);
+    }
     const int64_t b1 = (b0 + n) < a.batch ? (b0 + n) : a.batch;
 
     TileCtx ctx;
@@ -125,8 +159,10 @@ __global__ void __launch_bounds__(kCtaThreads, OCC) eb_fused_kernel(LaunchArgs a
     ctx.rows = fs.rows;
     ctx.nnz = fd.nnz;
     ctx.batch = a.batch;
-    ctx.out = a.out + fs.col_off;
+    ctx.out = reinterpret_cast<char*>(a.out);
     ctx.out_ld = a.out_ld;
+    ctx.out_dt = a.out_dtype;
+    ctx.es_shift = a.out_dtype ? 1 : 2;
     ctx.peer_out = hdr->peer_out;
     ctx.rows_per_peer = a.rows_per_peer;
     ctx.col_off = fs.col_off;
@@ -153,6 +189,19 @@ __global__ void __launch_bounds__(kCtaThreads, OCC) eb_fused_kernel(LaunchArgs a
       const long long c1 = clock64();
       if (lane == 0) atomicAdd(feat_ns + f, (unsigned long long)(c1 - c0));
     }
+    if (a.chunks > 0) {
+      // publish: every lane's stores first, then one count per tile; the last tile of a chunk raises its flag
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) {
+        ChunkSync* cs = reinterpret_cast<ChunkSync*>(a.ws + L.chunk_sync);
+        const uint32_t done = atomicAdd(&cs->done[chunk], 1u) + 1u;
+        if (done == per_chunk) {
+          __threadfence();
+          *reinterpret_cast<volatile uint32_t*>(&cs->flag[chunk]) = a.epoch;
+        }
+      }
+    }
     t = __shfl_sync(kFull, tn, 0);
   }
 }
@@ -163,6 +212,8 @@ __global__ void __launch_bounds__(kCtaThreads, OCC) eb_fused_kernel(LaunchArgs a
 #undef EB_DISPATCH_KIND64
 #undef EB_DISPATCH_PIPE
 #undef EB_DISPATCH_PIPE_T
+#undef EB_DISPATCH_STREAM
+#undef EB_DISPATCH_STREAM_T
 #undef EB_DISPATCH_DTYPE_U4
 
 }  // namespace ebk

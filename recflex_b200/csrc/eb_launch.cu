@@ -1,5 +1,7 @@
 // Launchers: pick the fused-kernel instantiation for an occupancy, launch the
 // binding kernel and the table-fill kernel.
+#include <atomic>
+
 #include "eb_bind.cuh"
 #include "eb_launch.h"
 
@@ -23,17 +25,37 @@ cudaError_t launch_bind(const LaunchArgs& a, bool zero_feature_times, cudaStream
   return cudaGetLastError();
 }
 
-// Dynamic shared memory above 48 KB must be opted into once per kernel function (and per device).
+cudaError_t launch_release(const LaunchArgs& a, cudaStream_t st) {
+  ChunkSync* cs = reinterpret_cast<ChunkSync*>(a.ws + ws_layout(a.num_features).chunk_sync);
+  eb_release_kernel<<<1, kMaxChunks, 0, st>>>(cs->flag, kMaxChunks, a.epoch);
+  return cudaGetLastError();
+}
+
+// Dynamic shared memory above 48 KB must be opted into once per kernel function and device.  The attribute call
+// is cheap and idempotent, so devices beyond the remembered range simply repeat it on every launch.
 static cudaError_t allow_smem(FusedKernel k, int occupancy, bool timing, size_t smem_bytes) {
-  static bool done[16][kMaxOccupancy + 1][2] = {};
+  constexpr int kRemembered = 64;
+  static std::atomic<bool> done[kRemembered][kMaxOccupancy + 1][2];
+  if (smem_bytes <= 48 * 1024) return cudaSuccess;
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
-  if (smem_bytes <= 48 * 1024 || dev >= 16 || done[dev][occupancy][timing ? 1 : 0]) return cudaSuccess;
+  const bool remember = dev >= 0 && dev < kRemembered;
+  if (remember && done[dev][occupancy][timing ? 1 : 0].load(std::memory_order_acquire)) return cudaSuccess;
   e = cudaFuncSetAttribute(reinterpret_cast<const void*>(k), cudaFuncAttributeMaxDynamicSharedMemorySize,
                            kPipeMaxCells * kPipeCellBytes * kWarpsPerCta);
-  if (e == cudaSuccess) done[dev][occupancy][timing ? 1 : 0] = true;
+  if (e == cudaSuccess && remember) done[dev][occupancy][timing ? 1 : 0].store(true, std::memory_order_release);
   return e;
+}
+
+// Grid of the grid-stride helper kernels: a few CTAs per SM of the current device.
+static int helper_grid(int64_t wanted, int ctas_per_sm) {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+    sms = 148;
+  const int64_t cap = (int64_t)sms * ctas_per_sm;
+  return (int)(wanted < 1 ? 1 : (wanted > cap ? cap : wanted));
 }
 
 cudaError_t launch_fused(const LaunchArgs& a, int occupancy, bool timing, int grid, size_t smem_bytes, cudaStream_t st) {
@@ -55,21 +77,18 @@ cudaError_t fused_ctas_per_sm(int occupancy, size_t smem_bytes, int* per_sm) {
 cudaError_t launch_fill(void* table, int64_t elems, int dtype, uint64_t seed, float std, cudaStream_t st) {
   // 65536 * sqrt(4 / 12): standard deviation of the centred sum of four 16-bit fields
   const float scale = std / 37837.227f;
-  int64_t blocks = (elems + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  const int blocks = helper_grid((elems + 255) / 256, 16);
   if (dtype == 1)
-    eb_fill_kernel<__half><<<(int)blocks, 256, 0, st>>>(static_cast<__half*>(table), elems, seed, scale);
+    eb_fill_kernel<__half><<<blocks, 256, 0, st>>>(static_cast<__half*>(table), elems, seed, scale);
   else
-    eb_fill_kernel<float><<<(int)blocks, 256, 0, st>>>(static_cast<float*>(table), elems, seed, scale);
+    eb_fill_kernel<float><<<blocks, 256, 0, st>>>(static_cast<float*>(table), elems, seed, scale);
   return cudaGetLastError();
 }
 
 cudaError_t launch_place(const float* src, float* dst, int64_t rows, int64_t dst_ld, int num_segments,
                          const void* segments, int vec_ok, cudaStream_t st) {
   if (rows == 0 || num_segments == 0) return cudaSuccess;
-  int64_t bx = (rows * 8 + 255) / 256;  // a few float4 per thread for the narrowest features
-  if (bx > 148 * 4) bx = 148 * 4;
-  if (bx < 1) bx = 1;
+  const int bx = helper_grid((rows * 8 + 255) / 256, 4);  // a few float4 per thread for the narrowest features
   for (int first = 0; first < num_segments; first += 65535) {
     const int n = num_segments - first < 65535 ? num_segments - first : 65535;
     eb_place_kernel<<<dim3((unsigned)bx, (unsigned)n), 256, 0, st>>>(

@@ -20,6 +20,8 @@ FusedKernel fused_kernel_occ7(bool timing);
 FusedKernel fused_kernel_occ8(bool timing);
 
 cudaError_t launch_bind(const LaunchArgs& a, bool zero_feature_times, cudaStream_t st);
+// Chunked ticket order: raises every chunk flag to the call's epoch once the fused kernel is done.
+cudaError_t launch_release(const LaunchArgs& a, cudaStream_t st);
 cudaError_t launch_fused(const LaunchArgs& a, int occupancy, bool timing, int grid, size_t smem_bytes, cudaStream_t st);
 // eb_warp_kernel: pools the `warp_features` features on the warp-per-bag schedule (one CTA per 8 bags).
 cudaError_t launch_warp(const LaunchArgs& a, bool timing, int warp_features, cudaStream_t st);

@@ -23,15 +23,20 @@
 //  - all calls on one GPU share the array, which keeps the previous call's
 //    contents; everything that must start from zero (ticket counters, status
 //    word) is re-initialised by the binding kernel of each call, and the
-//    descriptor table is rewritten by each call.  Two calls that overlap on the
-//    GPU (different streams, or different host threads) race on it: issue the
-//    calls for one GPU on one stream, or order the streams yourself;
+//    descriptor table is rewritten by each call.  Two calls whose kernels
+//    overlap on the GPU (different streams) race on it: issue the calls for
+//    one GPU on one stream, or order the streams yourself.  On the host, calls
+//    for one GPU are serialised by a lock and each GPU has its own staging
+//    buffer, so host threads driving different GPUs do not disturb each other;
 //  - the first call on each device looks up the array's device address
 //    (cudaGetSymbolAddress) and keeps it; make that first call outside any
-//    stream capture.
+//    stream capture;
+//  - every call stages its descriptors through host memory that the next call
+//    overwrites, so a call is refused while its stream is being captured.
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "../../include/recflex_b200.h"
 #include "eb_common.cuh"
@@ -42,12 +47,12 @@ using namespace ebk;
 namespace {
 
 constexpr int kMaxFeat = EB_NOALLOC_MAX_FEATURES;
-constexpr int kMaxDevices = 64;
+constexpr int kMaxDevices = 16;
 constexpr int kNoAllocOccupancy = 4;
 
 // descriptor table first, then a workspace laid out by ws_layout(kMaxFeat)
 constexpr size_t kDescBytes = sizeof(FeatStatic) * (size_t)kMaxFeat;
-constexpr size_t kWsBytesMax = sizeof(WsHeader) + 6 * 128 + (size_t)kMaxFeat * (4 + 4 + 4 + 4 + sizeof(FeatDyn) + 8) + 8;
+constexpr size_t kWsBytesMax = ws_layout(kMaxFeat).total;
 constexpr size_t kNoAllocScratchBytes = kDescBytes + ((kWsBytesMax + 255) / 256) * 256;
 
 // The name below is a host-side stand-in for the device array: host code must
@@ -58,8 +63,10 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratch
 char* g_scratch_ptr[kMaxDevices] = {};
 int g_sm_count[kMaxDevices] = {};
 
-// host staging of the descriptor table (pageable; cudaMemcpyAsync stages it before returning)
-FeatStatic g_host_feats[kMaxFeat];
+// host staging of the descriptor table, one per device (pageable: cudaMemcpyAsync has taken its copy when it
+// returns), filled and uploaded under that device's lock
+FeatStatic g_host_feats[kMaxDevices][kMaxFeat];
+std::mutex g_device_lock[kMaxDevices];
 
 // records the message where eb_last_error() finds it
 int fail(int code, const char* fmt, ...) {
@@ -123,11 +130,12 @@ int eb_forward_packed_noalloc(int device, int num_features, const int64_t* rows,
   if (!offsets || !out) return fail(EB_ERR_INVALID_ARG, "null offsets or output pointer");
   if ((reinterpret_cast<uintptr_t>(out) & 3) != 0) return fail(EB_ERR_INVALID_ARG, "output pointer is not 4-byte aligned");
 
+  std::lock_guard<std::mutex> lock(g_device_lock[device]);
   int64_t col = 0;
   for (int f = 0; f < num_features; ++f) {
     if (rows[f] <= 0 || dims[f] <= 0 || (table_dtype[f] != EB_F32 && table_dtype[f] != EB_F16) || !table_ptrs[f])
       return fail(EB_ERR_INVALID_ARG, "feature %d is not a valid table", f);
-    FeatStatic& fs = g_host_feats[f];
+    FeatStatic& fs = g_host_feats[device][f];
     memset(&fs, 0, sizeof(fs));
     const int esz = table_dtype[f] == EB_F16 ? 2 : 4;
     fs.table = static_cast<const char*>(table_ptrs[f]);
@@ -147,6 +155,7 @@ int eb_forward_packed_noalloc(int device, int num_features, const int64_t* rows,
     if (col > 0x7fffffff) return fail(EB_ERR_TOO_LARGE, "sum of dims exceeds 2^31");
   }
   if (out_ld < col) return fail(EB_ERR_INVALID_ARG, "out_ld %lld < output units %lld", (long long)out_ld, (long long)col);
+  if (out_ld >= (1ll << 30)) return fail(EB_ERR_TOO_LARGE, "out_ld %lld: output rows must stay below 2^30 elements", (long long)out_ld);
 
   int prev = -1;
   if (cudaGetDevice(&prev) != cudaSuccess) return fail(EB_ERR_CUDA, "cudaGetDevice failed");
@@ -157,7 +166,14 @@ int eb_forward_packed_noalloc(int device, int num_features, const int64_t* rows,
     rc = scratch_for(device, &scratch);
     if (rc != EB_OK) break;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    cudaError_t e = cudaMemcpyAsync(scratch, g_host_feats, sizeof(FeatStatic) * num_features, cudaMemcpyHostToDevice, st);
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    cudaError_t e = cudaStreamIsCapturing(st, &cap);
+    if (e != cudaSuccess) { rc = fail(EB_ERR_CUDA, "cudaStreamIsCapturing failed: %s", cudaGetErrorString(e)); break; }
+    if (cap != cudaStreamCaptureStatusNone) {
+      rc = fail(EB_ERR_UNSUPPORTED, "the stream is being captured: this call stages descriptors through host memory");
+      break;
+    }
+    e = cudaMemcpyAsync(scratch, g_host_feats[device], sizeof(FeatStatic) * num_features, cudaMemcpyHostToDevice, st);
     if (e != cudaSuccess) { rc = fail(EB_ERR_CUDA, "descriptor upload failed: %s", cudaGetErrorString(e)); break; }
     LaunchArgs a;
     memset(&a, 0, sizeof(a));
@@ -180,6 +196,31 @@ int eb_forward_packed_noalloc(int device, int num_features, const int64_t* rows,
     if (e != cudaSuccess) { rc = fail(EB_ERR_CUDA, "bind launch failed: %s", cudaGetErrorString(e)); break; }
     e = launch_fused(a, kNoAllocOccupancy, false, g_sm_count[device] * kNoAllocOccupancy, 0, st);
     if (e != cudaSuccess) { rc = fail(EB_ERR_CUDA, "fused launch failed: %s", cudaGetErrorString(e)); break; }
+  } while (0);
+  if (prev >= 0 && prev != device) cudaSetDevice(prev);
+  return rc;
+}
+
+int eb_noalloc_check_status(int device, void* stream) {
+  if (device < 0 || device >= kMaxDevices) return fail(EB_ERR_INVALID_ARG, "device %d out of range", device);
+  int prev = -1;
+  if (cudaGetDevice(&prev) != cudaSuccess) return fail(EB_ERR_CUDA, "cudaGetDevice failed");
+  if (prev != device && cudaSetDevice(device) != cudaSuccess) return fail(EB_ERR_CUDA, "cannot select device %d", device);
+  int rc = EB_OK;
+  do {
+    std::lock_guard<std::mutex> lock(g_device_lock[device]);
+    char* scratch = nullptr;
+    rc = scratch_for(device, &scratch);
+    if (rc != EB_OK) break;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    WsHeader hdr;
+    cudaError_t e = cudaMemcpyAsync(&hdr, scratch + kDescBytes, sizeof(hdr), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) { rc = fail(EB_ERR_CUDA, "reading the status word failed: %s", cudaGetErrorString(e)); break; }
+    if (hdr.status & kStatusBadIndex)
+      rc = fail(EB_ERR_BAD_INPUT, "an index outside [0, rows) was met and skipped");
+    else if (hdr.status & kStatusBadOffsets)
+      rc = fail(EB_ERR_BAD_INPUT, "offsets were not a non-decreasing sequence inside [0, nnz]; they were clamped");
   } while (0);
   if (prev >= 0 && prev != device) cudaSetDevice(prev);
   return rc;

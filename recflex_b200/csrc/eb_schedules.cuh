@@ -20,6 +20,8 @@
 // device templates (examples/csrc/include/*_kernel.cuh) but share one load/store
 // core, 64-bit row addressing, and write every bag of the tile (empty bags -> 0).
 #pragma once
+#include <cuda_bf16.h>
+
 #include "eb_common.cuh"
 
 namespace ebk {
@@ -33,11 +35,13 @@ struct TileCtx {
   int64_t rows;
   int64_t nnz;
   int64_t batch;
-  float* out;        // already advanced to the feature's first column (unused in peer mode)
-  int64_t out_ld;
+  char* out;         // output matrix (unused in peer mode); elements are fp32, or 2 bytes wide when out_dt != 0
+  int64_t out_ld;    // row length in elements
   float* const* peer_out;  // peer mode: every rank's output matrix
   int64_t rows_per_peer;   // 0 = single output matrix
-  int32_t col_off;
+  int32_t col_off;   // the feature's first column
+  int32_t out_dt;    // element type of the output: 0 = fp32, 1 = bfloat16, 2 = binary16
+  int32_t es_shift;  // log2 of the output element size: 2 or 1
   uint32_t* status;
   int32_t dim;
   int32_t row_bytes;
@@ -45,7 +49,7 @@ struct TileCtx {
   int32_t nx;
   bool idx64;
   bool has_end;
-  int out_vec;       // widest aligned store the output allows: 0 = scalar, 1 = 16 bytes, 2 = 32 bytes
+  int out_vec;       // widest aligned store the output allows: 0 = one element, 1 = four elements, 2 = eight elements
 };
 
 __device__ __forceinline__ int64_t load_index(const char* base, int64_t i, bool idx64) {
@@ -53,13 +57,13 @@ __device__ __forceinline__ int64_t load_index(const char* base, int64_t i, bool 
                : (int64_t)__ldg(reinterpret_cast<const int*>(base) + i);
 }
 
-// First output element (this feature's first column) of bag `bb`.  In peer mode
-// the bag's row lives in the output matrix of rank bb / rows_per_peer; chunks of
-// 32 bags never straddle two ranks because rows_per_peer is a multiple of 32.
-__device__ __forceinline__ float* chunk_out(const TileCtx& c, int64_t bb) {
-  if (c.rows_per_peer == 0) return c.out + bb * c.out_ld;
+// Address of this feature's first column in the row of bag `bb`.  In peer mode the bag's row lives in the
+// output matrix of rank bb / rows_per_peer; chunks of 32 bags never straddle two ranks because rows_per_peer is a
+// multiple of 32.
+__device__ __forceinline__ char* chunk_out(const TileCtx& c, int64_t bb) {
+  if (c.rows_per_peer == 0) return c.out + ((bb * c.out_ld + c.col_off) << c.es_shift);
   const int64_t d = bb / c.rows_per_peer;
-  return c.peer_out[d] + c.col_off + (bb - d * c.rows_per_peer) * c.out_ld;
+  return reinterpret_cast<char*>(c.peer_out[d]) + (((bb - d * c.rows_per_peer) * c.out_ld + c.col_off) << c.es_shift);
 }
 
 __device__ __forceinline__ void flag(uint32_t* status, uint32_t bit) {
@@ -133,8 +137,52 @@ struct RowOps<__half, 1> {
 // allows: two 16-byte stores would each cover only half of every 32-byte
 // sector, which L2 merges for local memory but which crosses NVLink as
 // half-filled packets when the destination is a peer's memory.
+// `dt` != 0 narrows the output: the fp32 sums are rounded to nearest even into bfloat16 (1) or binary16 (2)
+// elements, a lane's V values leaving as one 2 * V byte store when alignment allows (`ov` as for fp32).
+__device__ __forceinline__ unsigned pack_narrow(float lo, float hi, int dt) {
+  if (dt == 1) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const unsigned*>(&v);
+  }
+  const __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const unsigned*>(&v);
+}
+
+__device__ __forceinline__ float unpack_narrow(unsigned short bits, int dt) {
+  if (dt == 1) return __uint_as_float((unsigned)bits << 16);
+  return __half2float(__ushort_as_half(bits));
+}
+
 template <int V>
-__device__ __forceinline__ void store_vals(float* dst, const float (&a)[V], int vec_ok) {
+__device__ __forceinline__ void store_vals(char* dstb, const float (&a)[V], int vec_ok, int dt = 0) {
+  if (dt != 0) {
+    if constexpr (V == 1) {
+      const unsigned w = pack_narrow(a[0], 0.f, dt);
+      __stcs(reinterpret_cast<unsigned short*>(dstb), (unsigned short)(w & 0xffffu));
+    } else {
+      unsigned w[V / 2];
+#pragma unroll
+      for (int k = 0; k < V / 2; ++k) w[k] = pack_narrow(a[2 * k], a[2 * k + 1], dt);
+      if constexpr (V == 8) {
+        if (vec_ok == 2) {
+          __stcs(reinterpret_cast<uint4*>(dstb), make_uint4(w[0], w[1], w[2], w[3]));
+          return;
+        }
+      }
+      if (vec_ok) {
+#pragma unroll
+        for (int k = 0; k < V / 2; k += 2) __stcs(reinterpret_cast<uint2*>(dstb + 4 * k), make_uint2(w[k], w[k + 1]));
+      } else {
+#pragma unroll
+        for (int k = 0; k < V / 2; ++k) {
+          __stcs(reinterpret_cast<unsigned short*>(dstb + 4 * k), (unsigned short)(w[k] & 0xffffu));
+          __stcs(reinterpret_cast<unsigned short*>(dstb + 4 * k + 2), (unsigned short)(w[k] >> 16));
+        }
+      }
+    }
+    return;
+  }
+  float* dst = reinterpret_cast<float*>(dstb);
   if constexpr (V == 1) {
     __stcs(dst, a[0]);
   } else {
@@ -153,6 +201,35 @@ __device__ __forceinline__ void store_vals(float* dst, const float (&a)[V], int 
     } else {
 #pragma unroll
       for (int k = 0; k < V; ++k) __stcs(dst + k, a[k]);
+    }
+  }
+}
+
+// Read back what store_vals wrote (the head partial of a bag cut by a piece boundary) and add `add` to it.
+template <int V>
+__device__ __forceinline__ void reload_add(const char* srcb, const float (&add)[V], float (&res)[V], int vec_ok, int dt) {
+  if (dt != 0) {
+    const unsigned short* src = reinterpret_cast<const unsigned short*>(srcb);
+#pragma unroll
+    for (int k = 0; k < V; ++k) res[k] = unpack_narrow(src[k], dt) + add[k];
+    return;
+  }
+  const float* src = reinterpret_cast<const float*>(srcb);
+  if constexpr (V == 1) {
+    res[0] = src[0] + add[0];
+  } else {
+    if (vec_ok) {
+#pragma unroll
+      for (int k = 0; k < V; k += 4) {
+        const float4 q4 = *reinterpret_cast<const float4*>(src + k);
+        res[k] = q4.x + add[k];
+        res[k + 1] = q4.y + add[k + 1];
+        res[k + 2] = q4.z + add[k + 2];
+        res[k + 3] = q4.w + add[k + 3];
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < V; ++k) res[k] = src[k] + add[k];
     }
   }
 }
@@ -184,35 +261,76 @@ struct Chunk {
   int n;       // entries in the chunk
 };
 
-__device__ __forceinline__ Chunk load_chunk(const TileCtx& c, int64_t bb, int nb, int lane) {
-  const int li = lane <= nb ? lane : nb;
-  const int64_t a_raw = raw_offset(c, bb + li);
-  int64_t end_raw = __shfl_sync(kFull, a_raw, 31);
-  if (nb == 32) end_raw = raw_offset(c, bb + 32);
+// Slow path of load_chunk: force the sequence into shape and say so.
+static __device__ __noinline__ Chunk repair_chunk(const TileCtx& c, int64_t a_raw, int64_t end_raw, int lane) {
   int64_t m = clamp_off(a_raw, c.nnz);
   int64_t endm = clamp_off(end_raw, c.nnz);
-  bool bad = (m != a_raw) || (endm != end_raw);
 #pragma unroll
   for (int d = 1; d < 32; d <<= 1) {
     const int64_t t = __shfl_up_sync(kFull, m, d);
-    if (lane >= d && t > m) { m = t; bad = true; }
+    if (lane >= d && t > m) m = t;
   }
   const int64_t m31 = __shfl_sync(kFull, m, 31);
-  if (m31 > endm) { endm = m31; bad = true; }
+  if (m31 > endm) endm = m31;
   Chunk ch;
   ch.e0 = __shfl_sync(kFull, m, 0);
   int64_t nxt = __shfl_down_sync(kFull, m, 1);
   if (lane == 31) nxt = endm;
   int64_t total = endm - ch.e0;
-  if (total > 0x3fffffff) { total = 0x3fffffff; bad = true; }  // more than 2^30 indices in 32 bags: refuse the excess
+  if (total > 0x3fffffff) total = 0x3fffffff;  // more than 2^30 indices in 32 bags: refuse the excess
   int64_t lo = m - ch.e0, hi = nxt - ch.e0;
   if (lo > total) lo = total;
   if (hi > total) hi = total;
   ch.lo = (int)lo;
   ch.hi = (int)hi;
   ch.n = (int)total;
-  if (__any_sync(kFull, bad) && lane == 0) flag(c.status, kStatusBadOffsets);
+  if (lane == 0) flag(c.status, kStatusBadOffsets);
   return ch;
+}
+
+// One warp vote decides whether the 33 boundaries are already a non-decreasing sequence inside [0, nnz] spanning at
+// most 2^30 entries (the normal case: a handful of instructions, 32-bit when the batch's integers are); only
+// otherwise is the sequence repaired.  Must be called by all 32 lanes.
+template <bool IDX64>
+__device__ __forceinline__ Chunk load_chunk(const TileCtx& c, int64_t bb, int nb, int lane) {
+  const int li = lane <= nb ? lane : nb;
+  Chunk ch;
+  if constexpr (!IDX64) {
+    const int nnz = c.nnz > 0x7fffffff ? 0x7fffffff : (int)c.nnz;
+    const int* op = reinterpret_cast<const int*>(c.offsets);
+    const bool past = !c.has_end && bb + li >= c.batch;  // the one boundary an offsets array without end entry lacks
+    const int a = past ? nnz : __ldg(op + bb + li);
+    int end = __shfl_sync(kFull, a, 31);
+    if (nb == 32) end = (!c.has_end && bb + 32 >= c.batch) ? nnz : __ldg(op + bb + 32);
+    int nxt = __shfl_down_sync(kFull, a, 1);
+    if (lane == 31) nxt = end;
+    const int a0 = __shfl_sync(kFull, a, 0);
+    const bool good = a >= 0 && a <= nxt && nxt <= nnz && (unsigned)(end - a0) <= 0x3fffffffu;
+    if (__all_sync(kFull, good)) {
+      ch.e0 = a0;
+      ch.lo = a - a0;
+      ch.hi = nxt - a0;
+      ch.n = end - a0;
+      return ch;
+    }
+    return repair_chunk(c, (int64_t)a, (int64_t)end, lane);
+  } else {
+    const int64_t a = raw_offset(c, bb + li);
+    int64_t end = __shfl_sync(kFull, a, 31);
+    if (nb == 32) end = raw_offset(c, bb + 32);
+    int64_t nxt = __shfl_down_sync(kFull, a, 1);
+    if (lane == 31) nxt = end;
+    const int64_t a0 = __shfl_sync(kFull, a, 0);
+    const bool good = a >= 0 && a <= nxt && nxt <= c.nnz && end - a0 <= 0x3fffffff;
+    if (__all_sync(kFull, good)) {
+      ch.e0 = a0;
+      ch.lo = (int)(a - a0);
+      ch.hi = (int)(nxt - a0);
+      ch.n = (int)(end - a0);
+      return ch;
+    }
+    return repair_chunk(c, a, end, lane);
+  }
 }
 
 // Index element type of a batch.
@@ -295,8 +413,9 @@ __device__ __forceinline__ void tile_group(const TileCtx& c, int64_t b0, int64_t
     const char* tcol = c.table + (size_t)cs * sizeof(T);
     for (int64_t bb = b0; bb < b1; bb += 32) {
       const int nb = (int)((b1 - bb) < 32 ? (b1 - bb) : 32);
-      const Chunk ch = load_chunk(c, bb, nb, lane);
-      float* orow = chunk_out(c, bb) + cs;
+      const Chunk ch = load_chunk<IDX64>(c, bb, nb, lane);
+      char* orow = chunk_out(c, bb) + ((size_t)cs << c.es_shift);
+      const size_t row_b = (size_t)c.out_ld << c.es_shift;
       const typename IdxOf<IDX64>::type* vals = reinterpret_cast<const typename IdxOf<IDX64>::type*>(c.values) + ch.e0;
       for (int i0 = 0; i0 < nb; i0 += R) {
         const int bi = i0 + r;
@@ -319,7 +438,7 @@ __device__ __forceinline__ void tile_group(const TileCtx& c, int64_t b0, int64_t
 #pragma unroll
           for (int u = 0; u < U; ++u) Ops::add(acc, rows[u]);
         }
-        if (bi < nb && col_ok) store_vals<V>(orow + (int64_t)bi * c.out_ld, acc, c.out_vec);
+        if (bi < nb && col_ok) store_vals<V>(orow + (size_t)bi * row_b, acc, c.out_vec, c.out_dt);
       }
     }
   }
@@ -340,8 +459,9 @@ __device__ __forceinline__ void tile_warp(const TileCtx& c, int64_t b0, int64_t 
     const char* tcol = c.table + (size_t)cs * sizeof(T);
     for (int64_t bb = b0; bb < b1; bb += 32) {
       const int nb = (int)((b1 - bb) < 32 ? (b1 - bb) : 32);
-      const Chunk ch = load_chunk(c, bb, nb, lane);
-      float* orow = chunk_out(c, bb) + cs;
+      const Chunk ch = load_chunk<IDX64>(c, bb, nb, lane);
+      char* orow = chunk_out(c, bb) + ((size_t)cs << c.es_shift);
+      const size_t row_b = (size_t)c.out_ld << c.es_shift;
       const typename IdxOf<IDX64>::type* vals = reinterpret_cast<const typename IdxOf<IDX64>::type*>(c.values) + ch.e0;
       for (int i = 0; i < nb; ++i) {
         const int s = __shfl_sync(kFull, ch.lo, i);
@@ -368,7 +488,7 @@ __device__ __forceinline__ void tile_warp(const TileCtx& c, int64_t b0, int64_t 
             for (int k = 0; k < V; ++k) acc[k] += __shfl_xor_sync(kFull, acc[k], d);
           }
         }
-        if (r == 0 && col_ok) store_vals<V>(orow + (int64_t)i * c.out_ld, acc, c.out_vec);
+        if (r == 0 && col_ok) store_vals<V>(orow + (size_t)i * row_b, acc, c.out_vec, c.out_dt);
       }
     }
   }
@@ -394,8 +514,9 @@ __device__ __forceinline__ void tile_flat(const TileCtx& c, int64_t b0, int64_t 
     const char* tcol = c.table + (size_t)cs * sizeof(T);
     for (int64_t bb = b0; bb < b1; bb += 32) {
       const int nb = (int)((b1 - bb) < 32 ? (b1 - bb) : 32);
-      const Chunk ch = load_chunk(c, bb, nb, lane);
-      float* orow = chunk_out(c, bb) + cs;
+      const Chunk ch = load_chunk<IDX64>(c, bb, nb, lane);
+      char* orow = chunk_out(c, bb) + ((size_t)cs << c.es_shift);
+      const size_t row_b = (size_t)c.out_ld << c.es_shift;
       const typename IdxOf<IDX64>::type* vals = reinterpret_cast<const typename IdxOf<IDX64>::type*>(c.values) + ch.e0;
       const int n = ch.n;
       const bool nonempty = ch.hi > ch.lo;
@@ -409,7 +530,7 @@ __device__ __forceinline__ void tile_flat(const TileCtx& c, int64_t b0, int64_t 
         while (em) {
           // slot r takes the r-th remaining empty bag
           const int i = (int)__fns(em, 0, r + 1);  // -1 when fewer than r + 1 remain
-          if (i >= 0 && col_ok) store_vals<V>(orow + (int64_t)i * c.out_ld, z, c.out_vec);
+          if (i >= 0 && col_ok) store_vals<V>(orow + (size_t)i * row_b, z, c.out_vec, c.out_dt);
           // drop the R lowest set bits
           for (int k = 0; k < R && em; ++k) em &= em - 1;
         }
@@ -451,7 +572,7 @@ __device__ __forceinline__ void tile_flat(const TileCtx& c, int64_t b0, int64_t 
                     for (int k = 0; k < V; ++k) acc[k] += __shfl_xor_sync(kFull, acc[k], d);
                   }
                 }
-                if (r == 0 && col_ok) store_vals<V>(orow + (int64_t)wbag * c.out_ld, acc, c.out_vec);
+                if (r == 0 && col_ok) store_vals<V>(orow + (size_t)wbag * row_b, acc, c.out_vec, c.out_dt);
               }
               if (!inw) Ops::add(x, rows[u]);
 
@@ -492,7 +613,7 @@ __device__ __forceinline__ void tile_flat(const TileCtx& c, int64_t b0, int64_t 
                 if (is_head && !keeps && col_ok) {
                   const int q = __popc(head_mask & ((1u << r) - 1u));
                   const int mybag = __fns(head_bags, 0, q + 1);
-                  store_vals<V>(orow + (int64_t)mybag * c.out_ld, x, c.out_vec);
+                  store_vals<V>(orow + (size_t)mybag * row_b, x, c.out_vec, c.out_dt);
                 }
 #pragma unroll
                 for (int k = 0; k < V; ++k) acc[k] = keeps ? x[k] : 0.f;
@@ -568,40 +689,67 @@ __device__ __forceinline__ bool issue_rows(const TileCtx& c, const char* tcol, b
 }
 
 // ---------------------------------------------------------------------------
-// EB_SCHED_STREAM: the chunk's n entries are cut into R contiguous pieces of
-// ceil(n / R) entries, one per slot.  Every slot walks its piece serially with
-// U rows in flight, whatever the bag lengths: a bag that ends inside the piece
-// is stored at once (a warp vote guards the store path, so steps without a
-// boundary pay one vote).  While a whole macro-step of U entries stays inside
-// the current bag for every slot, the walk is a pure load + accumulate loop.
-// A bag cut by a piece boundary leaves a tail partial in the slot's
-// accumulator and a head partial in the output row; after the walk a segmented
-// shuffle scan over the slots' tails patches each head (once per 32 bags).
-// ---------------------------------------------------------------------------
+// EB_SCHED_STREAM: the chunk's n entries are cut into R contiguous pieces, one
+// per slot, of floor(n / R) or one more entries.  Every slot walks its piece
+// serially with U rows in flight, whatever the bag lengths: a bag that ends
+// inside the piece is stored at once.  While a whole macro-step of U entries
+// stays inside the current bag for every slot (one warp vote), the walk is a
+// pure load + accumulate loop.  A bag cut by a piece boundary leaves a tail
+// partial in the slot's accumulator and a head partial in the output row; after
+// the walk a segmented shuffle scan over the slots' tails patches each head
+// (once per 32 bags).
+//
+// What a slot needs at a bag end is the next non-empty bag and where it ends.
+// The chunk's non-empty bags are therefore listed once per chunk in shared
+// memory ({end, bag}, closed by a sentinel): non-empty bags are contiguous in
+// the entry stream, so the next list item starts where the current one ends,
+// and a bag end costs one store, one 8-byte shared load and no warp-wide
+// operation: slots that are not at a bag end simply skip the block.  An end
+// that lies beyond the slot's piece is replaced by a value no position reaches,
+// so entries past the piece's end (fetched as zeros) need no guard either.
 //
 // D > 0 selects the pipelined form (EB_SCHED_PIPE): the rows in flight live in a
 // per-warp shared-memory ring of D macro-steps (D * U * 512 bytes) filled by
 // per-lane cp.async copies instead of in registers, so D * U rows per lane are
 // in flight (against U) and the row registers are free; the walk, the stores
-// and the patch pass are the same.
+// and the patch pass are the same.  Macro-steps in which every slot has U real
+// entries with valid indices (two uniform tests) issue their copies without any
+// predicate; only the ragged end of a piece and bad input take the checked path.
+// ---------------------------------------------------------------------------
+constexpr int kBagItems = 34;        // per-warp list of a chunk's non-empty bags: 32 + sentinel, padded
+constexpr int kNoEnd = 0x7fffffff;   // "this bag does not end inside my piece"
+
+// Next list item; an end beyond the piece never matches a position.
+__device__ __forceinline__ void next_bag(unsigned& item_addr, int e_end, int& kb, int& kend) {
+  item_addr += 8;
+  int end;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(end), "=r"(kb) : "r"(item_addr));
+  kend = end > e_end ? kNoEnd : end;
+}
+
 template <typename T, int V, int U, bool IDX64, int D = 0>
-__device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_t b1, int lane,
+__device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_t b1, int lane, int2* items,
                                             unsigned char* ring = nullptr) {
   static_assert(D == 0 || V * sizeof(T) == 16, "the ring holds 16-byte lane cells");
   using Ops = RowOps<T, V>;
   using IdxT = typename IdxOf<IDX64>::type;
   const int lgG = c.lg_group, lgR = 5 - lgG, G = 1 << lgG, R = 1 << lgR;
   const int r = lane >> lgG, cl = lane & (G - 1);
+  const unsigned ld_bytes = (unsigned)c.out_ld << c.es_shift;  // the entry points refuse rows of 4 GB and more
+  const int dt = c.out_dt;
+  const unsigned rows32 = c.rows > 0x80000000ll ? 0x80000000u : (unsigned)c.rows;
+  const int ov = c.out_vec;
   for (int xc = 0; xc < c.nx; ++xc) {
     const int cs = (xc * G + cl) * V;
     const bool col_ok = cs < c.dim;
     const char* tcol = c.table + (size_t)cs * sizeof(T);
     for (int64_t bb = b0; bb < b1; bb += 32) {
       const int nb = (int)((b1 - bb) < 32 ? (b1 - bb) : 32);
-      const Chunk ch = load_chunk(c, bb, nb, lane);
+      const Chunk ch = load_chunk<IDX64>(c, bb, nb, lane);
       const int n = ch.n;
-      float* orow = chunk_out(c, bb) + cs;
-      const unsigned nz = __ballot_sync(kFull, ch.hi > ch.lo);
+      char* const orow = chunk_out(c, bb) + ((size_t)cs << c.es_shift);
+      const bool nonempty = ch.hi > ch.lo;
+      const unsigned nz = __ballot_sync(kFull, nonempty);
 
       // empty bags pool to zero: slot r takes the r-th remaining one
       {
@@ -611,16 +759,24 @@ __device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_
         zero_vals<V>(z);
         while (em) {
           const int i = (int)__fns(em, 0, r + 1);
-          if (i >= 0 && col_ok) store_vals<V>(orow + (int64_t)i * c.out_ld, z, c.out_vec);
+          if (i >= 0 && col_ok) store_vals<V>(orow + (size_t)i * ld_bytes, z, ov, dt);
           for (int k = 0; k < R && em; ++k) em &= em - 1;
         }
       }
       if (n == 0) continue;
 
-      // my piece [s, e_end) and the bag that holds its first entry
-      const int ls = (n + R - 1) >> lgR;
-      const int s = min(r * ls, n);
-      const int e_end = min(s + ls, n);
+      // the chunk's non-empty bags, in order
+      __syncwarp();  // nobody still reads the previous chunk's list
+      if (nonempty) items[__popc(nz & ((1u << lane) - 1u))] = make_int2(ch.hi, lane);
+      if (lane == 0) items[__popc(nz)] = make_int2(kNoEnd, 0);
+      __syncwarp();
+
+      // my piece [s, e_end): the first n % R slots hold one entry more
+      const int q = n >> lgR, rem = n & (R - 1);
+      const int s = r * q + min(r, rem);
+      const int e_end = s + q + (r < rem ? 1 : 0);
+      const int ls = q + (rem ? 1 : 0);  // longest piece; the shortest has q entries
+      // the bag that holds my first entry
       int kb = 0;
 #pragma unroll
       for (int step = 16; step >= 1; step >>= 1) {
@@ -628,9 +784,13 @@ __device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_
         if (t <= s) kb += step;
       }
       int kend = __shfl_sync(kFull, ch.hi, kb);
-      bool head_pending = __shfl_sync(kFull, ch.lo, kb) < s;  // my first bag began in an earlier piece
-      bool had_head = false;
-      int head_bag = 0;
+      const int klo = __shfl_sync(kFull, ch.lo, kb);
+      unsigned item_addr = smem_addr(items) + 8u * (unsigned)__popc(nz & ((1u << kb) - 1u));  // its place in the list
+      const bool began_earlier = klo < s && e_end > s;
+      const bool had_head = began_earlier && kend <= e_end;  // it ends inside my piece: its first part lies in earlier pieces
+      const bool inside_one = began_earlier && kend > e_end;  // my whole piece lies inside one bag
+      const int head_bag = kb;
+      if (kend > e_end) kend = kNoEnd;
       int e = s;
       const IdxT* vp = reinterpret_cast<const IdxT*>(c.values) + ch.e0;
       float acc[V];
@@ -641,41 +801,26 @@ __device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_
           int p[U];
           bool ok[U];
           typename Ops::Raw rows[U];
-  #pragma unroll
+#pragma unroll
           for (int u = 0; u < U; ++u) {
             p[u] = e + u;
             ok[u] = p[u] < e_end;
           }
-          const bool inner = (e + U < kend) && (e + U <= e_end);
-          if (__all_sync(kFull, inner)) {
-            fetch_rows<T, V, U, IDX64, false>(c, vp, tcol, col_ok, p, ok, rows);
-  #pragma unroll
+          if (k + U <= q) fetch_rows<T, V, U, IDX64, false>(c, vp, tcol, col_ok, p, ok, rows);
+          else fetch_rows<T, V, U, IDX64, true>(c, vp, tcol, col_ok, p, ok, rows);
+          if (__all_sync(kFull, e + U < kend)) {
+#pragma unroll
             for (int u = 0; u < U; ++u) Ops::add(acc, rows[u]);
             e += U;
           } else {
-            fetch_rows<T, V, U, IDX64, true>(c, vp, tcol, col_ok, p, ok, rows);
-  #pragma unroll
+#pragma unroll
             for (int u = 0; u < U; ++u) {
               Ops::add(acc, rows[u]);
-              const bool at_end = ok[u] && (e + 1 == kend);
-              if (__any_sync(kFull, at_end)) {
-                const unsigned rest = kb >= 31 ? 0u : (nz & (0xfffffffeu << kb));
-                const int nkb = rest ? (__ffs(rest) - 1) : 31;
-                int nend = __shfl_sync(kFull, ch.hi, nkb);
-                if (!rest) nend = 0x7fffffff;
-                if (at_end) {
-                  if (col_ok) store_vals<V>(orow + (int64_t)kb * c.out_ld, acc, c.out_vec);
-                  if (head_pending) {
-                    had_head = true;
-                    head_bag = kb;
-                    head_pending = false;
-                  }
-                  zero_vals<V>(acc);
-                  kb = nkb;
-                  kend = nend;
-                }
+              if (++e == kend) {
+                if (col_ok) store_vals<V>(orow + (size_t)((unsigned)kb * (uint64_t)ld_bytes), acc, ov, dt);
+                zero_vals<V>(acc);
+                next_bag(item_addr, e_end, kb, kend);
               }
-              e += ok[u] ? 1 : 0;
             }
           }
         }
@@ -684,29 +829,62 @@ __device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_
         const int nsteps = (ls + U - 1) / U;
         IdxT idx[U];
         bool bad = false;
-        load_indices<U, IDX64>(vp, s, e_end, col_ok, idx);
-#pragma unroll
-        for (int pm = 0; pm < D - 1; ++pm) {  // fill the pipeline
-          bad |= issue_rows<T, U, IDX64>(c, tcol, col_ok, idx, s + pm * U, e_end, cell + pm * U * 512);
-          cp_async_commit();
-          load_indices<U, IDX64>(vp, s + (pm + 1) * U, e_end, col_ok, idx);
-        }
-        unsigned cell_in = cell + (D - 1) * U * 512, cell_out = cell;  // ring cursors
-        const unsigned cell_end = cell + D * U * 512;
-        for (int m = 0; m < nsteps; ++m) {
-          bad |= issue_rows<T, U, IDX64>(c, tcol, col_ok, idx, s + (m + D - 1) * U, e_end, cell_in);
-          cp_async_commit();
-          load_indices<U, IDX64>(vp, s + (m + D) * U, e_end, col_ok, idx);  // indices one macro-step ahead of their copies
-          cp_async_wait<D - 1>();
-          bool ok[U];
-          typename Ops::Raw rows[U];
+        // indices of macro-step 0; `plain`: every slot has U real entries there and every index is a row of the table
+        bool plain = false;
+        if (U <= q) {
+          bool valid = true;
 #pragma unroll
           for (int u = 0; u < U; ++u) {
-            ok[u] = e + u < e_end;
-            rows[u] = lds16(cell_out + u * 512);
+            idx[u] = __ldg(vp + s + u);
+            if constexpr (IDX64) valid = valid && (uint64_t)idx[u] < (uint64_t)c.rows;
+            else valid = valid && (unsigned)idx[u] < rows32;
           }
-          const bool inner = (e + U < kend) && (e + U <= e_end);
-          if (__all_sync(kFull, inner)) {
+          plain = __all_sync(kFull, valid);
+        } else {
+          load_indices<U, IDX64>(vp, s, e_end, col_ok, idx);
+        }
+        unsigned cell_in = cell, cell_out = cell;  // ring cursors
+        const unsigned cell_end = cell + D * U * 512;
+        // iteration m issues the copies of macro-step m + D - 1, fetches the indices of macro-step m + D and, from
+        // m = 0 on, consumes macro-step m
+#pragma unroll 1
+        for (int m = 1 - D; m < nsteps; ++m) {
+          const int first = s + (m + D - 1) * U;
+          if (m + D - 1 >= nsteps) {
+            // past every piece's end: an empty copy group keeps the group count in step
+          } else if (plain) {
+            if (col_ok) {
+#pragma unroll
+              for (int u = 0; u < U; ++u) {
+                if constexpr (IDX64) cp_async16(cell_in + u * 512, tcol + idx[u] * (int64_t)c.row_bytes, 16u);
+                else cp_async16(cell_in + u * 512, tcol + (uint64_t)(unsigned)idx[u] * (unsigned)c.row_bytes, 16u);
+              }
+            }
+          } else {
+            bad |= issue_rows<T, U, IDX64>(c, tcol, col_ok, idx, first, e_end, cell_in);
+          }
+          cp_async_commit();
+          if ((m + D + 1) * U <= q) {
+            bool valid = true;
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              idx[u] = __ldg(vp + first + U + u);
+              if constexpr (IDX64) valid = valid && (uint64_t)idx[u] < (uint64_t)c.rows;
+              else valid = valid && (unsigned)idx[u] < rows32;
+            }
+            plain = __all_sync(kFull, valid);
+          } else {
+            if (m + D < nsteps) load_indices<U, IDX64>(vp, first + U, e_end, col_ok, idx);
+            plain = false;
+          }
+          cell_in += U * 512;
+          if (cell_in == cell_end) cell_in = cell;
+          if (m < 0) continue;
+          cp_async_wait<D - 1>();
+          typename Ops::Raw rows[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) rows[u] = lds16(cell_out + u * 512);
+          if (__all_sync(kFull, e + U < kend)) {
 #pragma unroll
             for (int u = 0; u < U; ++u) Ops::add(acc, rows[u]);
             e += U;
@@ -714,29 +892,13 @@ __device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_
 #pragma unroll
             for (int u = 0; u < U; ++u) {
               Ops::add(acc, rows[u]);
-              const bool at_end = ok[u] && (e + 1 == kend);
-              if (__any_sync(kFull, at_end)) {
-                const unsigned rest = kb >= 31 ? 0u : (nz & (0xfffffffeu << kb));
-                const int nkb = rest ? (__ffs(rest) - 1) : 31;
-                int nend = __shfl_sync(kFull, ch.hi, nkb);
-                if (!rest) nend = 0x7fffffff;
-                if (at_end) {
-                  if (col_ok) store_vals<V>(orow + (int64_t)kb * c.out_ld, acc, c.out_vec);
-                  if (head_pending) {
-                    had_head = true;
-                    head_bag = kb;
-                    head_pending = false;
-                  }
-                  zero_vals<V>(acc);
-                  kb = nkb;
-                  kend = nend;
-                }
+              if (++e == kend) {
+                if (col_ok) store_vals<V>(orow + (size_t)((unsigned)kb * (uint64_t)ld_bytes), acc, ov, dt);
+                zero_vals<V>(acc);
+                next_bag(item_addr, e_end, kb, kend);
               }
-              e += ok[u] ? 1 : 0;
             }
           }
-          cell_in += U * 512;
-          if (cell_in == cell_end) cell_in = cell;
           cell_out += U * 512;
           if (cell_out == cell_end) cell_out = cell;
         }
@@ -746,7 +908,7 @@ __device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_
 
       // patch the bags cut by piece boundaries
       if (R > 1 && __any_sync(kFull, had_head)) {
-        bool f = !(head_pending && e_end > s);  // my tail starts a new run unless my whole piece lies inside one bag
+        bool f = !inside_one;  // my tail starts a new run unless my whole piece lies inside one bag
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
           if (d < R) {
@@ -764,26 +926,10 @@ __device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_
 #pragma unroll
         for (int k = 0; k < V; ++k) prev[k] = __shfl_up_sync(kFull, acc[k], G);
         if (had_head && col_ok) {
-          float* dst = orow + (int64_t)head_bag * c.out_ld;
+          char* dst = orow + (size_t)((unsigned)head_bag * (uint64_t)ld_bytes);
           float hv[V];
-          if constexpr (V == 1) {
-            hv[0] = dst[0] + prev[0];
-          } else {
-            if (c.out_vec) {
-#pragma unroll
-              for (int k = 0; k < V; k += 4) {
-                const float4 q = *reinterpret_cast<const float4*>(dst + k);
-                hv[k] = q.x + prev[k];
-                hv[k + 1] = q.y + prev[k + 1];
-                hv[k + 2] = q.z + prev[k + 2];
-                hv[k + 3] = q.w + prev[k + 3];
-              }
-            } else {
-#pragma unroll
-              for (int k = 0; k < V; ++k) hv[k] = dst[k] + prev[k];
-            }
-          }
-          store_vals<V>(dst, hv, c.out_vec);
+          reload_add<V>(dst, prev, hv, ov, dt);
+          store_vals<V>(dst, hv, ov, dt);
         }
       }
     }

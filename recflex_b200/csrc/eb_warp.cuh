@@ -83,8 +83,8 @@ __device__ __forceinline__ AccPack<V> bag_sum(const typename IdxOf<IDX64>::type*
 
 // One bag, one warp.
 template <typename T, int V, int U, bool IDX64>
-__device__ __forceinline__ void bag_warp(const FeatStatic& fs, const char* values, int64_t s, int64_t e, float* orow,
-                                         int out_vec, uint32_t* status, int lane) {
+__device__ __forceinline__ void bag_warp(const FeatStatic& fs, const char* values, int64_t s, int64_t e, char* orow,
+                                         int out_vec, int out_dt, uint32_t* status, int lane) {
   const int lgG = fs.lg_group, G = 1 << lgG, R = 32 >> lgG;
   const int r = lane >> lgG, cl = lane & (G - 1);
   const int len = (int)(e - s);
@@ -109,7 +109,7 @@ __device__ __forceinline__ void bag_warp(const FeatStatic& fs, const char* value
         for (int k = 0; k < V; ++k) a.v[k] += __shfl_xor_sync(kFull, a.v[k], d);
       }
     }
-    if (r == 0 && col_ok) store_vals<V>(orow + cs, a.v, out_vec);  // an empty bag stores zeros
+    if (r == 0 && col_ok) store_vals<V>(orow + ((size_t)cs << (out_dt ? 1 : 2)), a.v, out_vec, out_dt);  // an empty bag stores zeros
   }
 }
 
@@ -152,25 +152,26 @@ __global__ void __launch_bounds__(kCtaThreads, kWarpKernelOccupancy) eb_warp_ker
   if (e - s > 0x3fffffff) e = s + 0x3fffffff;
   if ((s != s0 || e != e0) && lane == 0) flag(&hdr->status, kStatusBadOffsets);
 
-  float* orow;
+  const int es_shift = a.out_dtype ? 1 : 2;
+  char* orow;
   if (a.rows_per_peer == 0) {
-    orow = a.out + bag * a.out_ld + fs.col_off;
+    orow = reinterpret_cast<char*>(a.out) + ((bag * a.out_ld + fs.col_off) << es_shift);
   } else {
     const int64_t d = bag / a.rows_per_peer;
-    orow = hdr->peer_out[d] + (bag - d * a.rows_per_peer) * a.out_ld + fs.col_off;
+    orow = reinterpret_cast<char*>(hdr->peer_out[d]) + (((bag - d * a.rows_per_peer) * a.out_ld + fs.col_off) << es_shift);
   }
   const int out_vec = (a.out_vec == 2 && (fs.col_off & 7) == 0) ? 2 : ((a.out_vec != 0 && (fs.col_off & 3) == 0) ? 1 : 0);
   uint32_t* status = &hdr->status;
   const bool u2 = fs.unroll <= 2;  // two or four rows per lane in flight
   if (idx64) {
-    if (fs.dtype == 1) bag_warp<__half, 8, 2, true>(fs, fd.values, s, e, orow, out_vec, status, lane);
-    else bag_warp<float, 4, 2, true>(fs, fd.values, s, e, orow, out_vec, status, lane);
+    if (fs.dtype == 1) bag_warp<__half, 8, 2, true>(fs, fd.values, s, e, orow, out_vec, a.out_dtype, status, lane);
+    else bag_warp<float, 4, 2, true>(fs, fd.values, s, e, orow, out_vec, a.out_dtype, status, lane);
   } else if (fs.dtype == 1) {
-    if (u2) bag_warp<__half, 8, 2, false>(fs, fd.values, s, e, orow, out_vec, status, lane);
-    else bag_warp<__half, 8, 4, false>(fs, fd.values, s, e, orow, out_vec, status, lane);
+    if (u2) bag_warp<__half, 8, 2, false>(fs, fd.values, s, e, orow, out_vec, a.out_dtype, status, lane);
+    else bag_warp<__half, 8, 4, false>(fs, fd.values, s, e, orow, out_vec, a.out_dtype, status, lane);
   } else {
-    if (u2) bag_warp<float, 4, 2, false>(fs, fd.values, s, e, orow, out_vec, status, lane);
-    else bag_warp<float, 4, 4, false>(fs, fd.values, s, e, orow, out_vec, status, lane);
+    if (u2) bag_warp<float, 4, 2, false>(fs, fd.values, s, e, orow, out_vec, a.out_dtype, status, lane);
+    else bag_warp<float, 4, 4, false>(fs, fd.values, s, e, orow, out_vec, a.out_dtype, status, lane);
   }
   if (TIMING) {
     __syncwarp();

@@ -108,11 +108,12 @@ class FeatEmbed(nn.Module):
         ws = C.c_size_t()
         _lib.check(self._lib.eb_workspace_bytes(self._h, C.byref(ws)))
         self._ws_bytes = int(ws.value)
-        self._ws = torch.empty(self._ws_bytes + 128, dtype=torch.uint8, device=self.device)
+        self._ws = torch.zeros(self._ws_bytes + 128, dtype=torch.uint8, device=self.device)  # chunk flags start at 0
         self._ws_ptr = (self._ws.data_ptr() + 127) // 128 * 128
         self._staging = None
         self._staging_ptr = 0
         self._staging_bytes = 0
+        self.output_dtype = torch.float32
 
     def __del__(self):
         # may run while the interpreter shuts down, when nn.Module's attribute machinery is already gone
@@ -145,6 +146,25 @@ class FeatEmbed(nn.Module):
         occ = C.c_int()
         _lib.check(self._lib.eb_get_schedules(self._h, arr, C.byref(occ)))
         return [Schedule(s.kind, s.unroll, s.bags_per_tile) for s in arr], int(occ.value)
+
+    _OUT_DTYPES = {torch.float32: _lib.EB_OUT_F32, torch.bfloat16: _lib.EB_OUT_BF16, torch.float16: _lib.EB_OUT_F16}
+
+    def set_output_dtype(self, dtype: torch.dtype) -> None:
+        """Element type of the pooled output: torch.float32 (default, the reference's contract), or torch.bfloat16 /
+        torch.float16 for consumers that cast anyway (sums are still accumulated in fp32 and rounded once on the
+        way out).  Output tensors passed as `out=` must then have this dtype."""
+        if dtype not in self._OUT_DTYPES:
+            raise TypeError(f"output dtype must be float32, bfloat16 or float16, got {dtype}")
+        _lib.check(self._lib.eb_set_output_dtype(self._h, self._OUT_DTYPES[dtype]))
+        self.output_dtype = dtype
+
+    def _check_out(self, out: Optional[torch.Tensor], batch: int) -> torch.Tensor:
+        if out is None:
+            return torch.empty((batch, self.output_units), dtype=self.output_dtype, device=self.device)
+        if out.dtype != self.output_dtype or out.dim() != 2 or out.shape[0] != batch or out.stride(1) != 1 \
+                or out.shape[1] < self.output_units:
+            raise ValueError(f"out must be a {self.output_dtype} [batch, >= output_units] tensor with unit column stride")
+        return out
 
     # -- forward -----------------------------------------------------------
     def _stream(self) -> C.c_void_p:
@@ -197,11 +217,7 @@ class FeatEmbed(nn.Module):
                 o = o.contiguous()
             keep.append((v, o))
             vp[f], op[f], nnz[f] = v.data_ptr(), o.data_ptr(), v.numel()
-        if out is None:
-            out = torch.empty((batch, self.output_units), dtype=torch.float32, device=self.device)
-        elif out.dtype != torch.float32 or out.dim() != 2 or out.shape[0] != batch or out.stride(1) != 1 \
-                or out.shape[1] < self.output_units:
-            raise ValueError("out must be an fp32 [batch, >= output_units] tensor with unit column stride")
+        out = self._check_out(out, batch)
         ld = out.stride(0) if batch > 1 else max(out.shape[1], self.output_units)
         if not timing:
             _lib.check(self._lib.eb_forward(self._h, batch, vp, op, nnz, idt, int(include_last_offset),
@@ -262,6 +278,39 @@ class FeatEmbed(nn.Module):
         _lib.check(self._lib.eb_forward_peers(self._h, batch, vp, op, nnz, idt, 1, pp, W, int(out_ld),
                                               C.c_void_p(self._ws_ptr), self._ws_bytes, self._stream()))
 
+    def _feature_pointers(self, values, offsets):
+        F = self.num_features
+        idt = self._index_dtype(values[0])
+        batch = offsets[0].numel() - 1
+        vp = (C.c_void_p * F)()
+        op = (C.c_void_p * F)()
+        nnz = (C.c_int64 * F)()
+        for f in range(F):
+            v, o = values[f], offsets[f]
+            if self._index_dtype(v) != idt or self._index_dtype(o) != idt:
+                raise TypeError("all values and offsets tensors must share one integer dtype")
+            if o.numel() != batch + 1 or not v.is_contiguous() or not o.is_contiguous():
+                raise ValueError(f"feature {f}: offsets need batch + 1 entries; tensors must be contiguous")
+            if v.device != self.device or o.device != self.device:
+                raise ValueError(f"feature {f}: values/offsets must live on {self.device}")
+            vp[f], op[f], nnz[f] = v.data_ptr(), o.data_ptr(), v.numel()
+        return idt, batch, vp, op, nnz
+
+    def forward_exchange(self, values: Sequence[torch.Tensor], offsets: Sequence[torch.Tensor], send: torch.Tensor,
+                         peer_ptrs: Sequence[int], rank: int, out_ld: int, out_col: int, chunks: int,
+                         copy_stream: torch.cuda.Stream) -> None:
+        """Pooling + copy-engine exchange (see eb_forward_exchange in include/recflex_b200.h): pools the whole batch
+        into `send` ([batch, >= output_units], this module's output dtype) piece by piece and lets `copy_stream`
+        ship every finished piece to the ranks' matrices `peer_ptrs` at columns [out_col, out_col + output_units)."""
+        idt, batch, vp, op, nnz = self._feature_pointers(values, offsets)
+        send = self._check_out(send, batch)
+        W = len(peer_ptrs)
+        pp = (C.c_void_p * W)(*[int(p) for p in peer_ptrs])
+        _lib.check(self._lib.eb_forward_exchange(self._h, batch, vp, op, nnz, idt, 1, C.c_void_p(send.data_ptr()),
+                                                 send.stride(0), pp, W, int(rank), int(out_ld), int(out_col),
+                                                 int(chunks), C.c_void_p(self._ws_ptr), self._ws_bytes, self._stream(),
+                                                 C.c_void_p(copy_stream.cuda_stream)))
+
     def forward_packed(self, values: torch.Tensor, offsets: torch.Tensor, out: Optional[torch.Tensor] = None):
         """Same forward for one packed batch: `values` = all features' indices back to back,
         `offsets` = `[num_features, batch + 1]`, both on the device."""
@@ -271,8 +320,7 @@ class FeatEmbed(nn.Module):
         if self._index_dtype(offsets) != idt:
             raise TypeError("values and offsets must share one integer dtype")
         batch = offsets.shape[1] - 1
-        if out is None:
-            out = torch.empty((batch, self.output_units), dtype=torch.float32, device=self.device)
+        out = self._check_out(out, batch)
         ld = out.stride(0) if batch > 1 else max(out.shape[1], self.output_units)
         _lib.check(self._lib.eb_forward_packed(self._h, batch, C.c_void_p(values.data_ptr()),
                                                C.c_void_p(offsets.data_ptr()), idt, C.c_void_p(out.data_ptr()), ld,
@@ -302,7 +350,10 @@ class FeatEmbed(nn.Module):
         idt = self._index_dtype(values)
         batch = offsets.shape[1] - 1
         if out is None:
-            out = torch.empty((batch, self.output_units), dtype=torch.float32, pin_memory=True)
+            out = torch.empty((batch, self.output_units), dtype=self.output_dtype, pin_memory=True)
+        elif out.dtype != self.output_dtype or out.is_cuda or not out.is_contiguous() \
+                or out.numel() != batch * self.output_units:
+            raise ValueError(f"out must be a contiguous host {self.output_dtype} [batch, output_units] tensor")
         need = C.c_size_t()
         _lib.check(self._lib.eb_host_staging_bytes(self._h, batch, values.numel(), idt, C.byref(need)))
         if self._staging_bytes < need.value:
@@ -397,17 +448,23 @@ class FeatProcessEmbed(nn.Module):
 
 
 class RecomModel(nn.Module):
-    """Fused embedding + MLP (reference: rec_modules.py:143-179): embed -> [batch, output_units] -> MLP -> sigmoid."""
+    """Fused embedding + MLP (reference: rec_modules.py:143-179): embed -> [batch, output_units] -> MLP -> sigmoid.
+
+    `mlp_dtype` (not in the reference, whose model is fp32 throughout) selects the MLP's precision.  With
+    torch.bfloat16 or torch.float16 the embedding layer writes its pooled sums directly in that type
+    (`FeatEmbed.set_output_dtype`), i.e. in the first linear layer's input layout and dtype: no fp32 intermediate is
+    written or re-read, and the cast costs nothing."""
 
     def __init__(self, mlp_unit_nums: List[int], device, embed_tables: Optional[List[torch.Tensor]] = None,
-                 table_shapes: Optional[Sequence[Tuple[int, int]]] = None):
+                 table_shapes: Optional[Sequence[Tuple[int, int]]] = None, mlp_dtype: torch.dtype = torch.float32):
         super().__init__()
         self.device = torch.device("cuda", _device_index(device))
         self.embed_layer = FeatEmbed(device=self.device, embed_tables=embed_tables, table_shapes=table_shapes)
+        self.embed_layer.set_output_dtype(mlp_dtype)
         layers = []
         unit_nums = [self.embed_layer.output_units] + list(mlp_unit_nums) + [1]
         for i in range(len(unit_nums) - 1):
-            layers.append(nn.Linear(unit_nums[i], unit_nums[i + 1], bias=True, device=self.device))
+            layers.append(nn.Linear(unit_nums[i], unit_nums[i + 1], bias=True, device=self.device, dtype=mlp_dtype))
             layers.append(nn.Sigmoid() if i + 2 == len(unit_nums) else nn.ReLU())
         self.mlp = nn.Sequential(*layers)
 

@@ -11,17 +11,25 @@ RecFlex/tuning/measure.py:27,68); both modes here are new:
   every feature's columns at its canonical position, so that rank r ends with `[B / world, sum(dim)]` for
   its share of the samples, identical to what the unsharded module computes for those samples.
 
-Two exchanges are implemented.  `exchange="peer"` (default on GPUs) is the fused one: the outputs of all ranks
-live in buffers every rank has mapped (CUDA IPC over NVLink), and the fused kernel stores each pooled row straight
-into the destination rank's final matrix at the feature's canonical columns, so the transfer overlaps the pooling
-tile by tile and no send buffer, all-to-all or placement pass exists; a one-element all-reduce on the same stream
-tells every rank that all kernels are done.  `exchange="nccl"` is the library baseline: pool into a send buffer,
-`all_to_all_single`, placement kernel.
+Three exchanges are implemented.  `exchange="peer"` is the fused one: the outputs of all ranks live in buffers
+every rank has mapped (CUDA IPC over NVLink), and the fused kernel stores each pooled row straight into the
+destination rank's final matrix at the feature's canonical columns, so the transfer overlaps the pooling tile by
+tile and no send buffer, all-to-all or placement pass exists; a one-element all-reduce on the same stream tells
+every rank that all kernels are done.  It hides the transfer completely at 2 and 4 GPUs.  `exchange="copy"` is for
+8 GPUs, where 7/8 of every pooled row leaves the GPU and plain stores of 64 to 512 bytes use NVLink less well than
+the copy engines do: the kernel pools into a local send buffer in ONE launch whose tile order walks the batch piece
+by piece, and a copy stream ships every finished piece as one 2-D copy per destination (rows of sum(local dims)
+elements) while the next piece is pooled (`eb_forward_exchange`).  Its result has the columns grouped by owner rank
+(`column_of[f]` says where feature f starts); `columns="canonical"` adds a placement pass that restores feature
+order.  `exchange="nccl"` is the library baseline: pool into a send buffer, `all_to_all_single`, placement kernel.
 
 With `exchange="nccl"`, batch chunks pipeline the exchange behind the pooling: chunk k's all-to-all runs on a side stream
 while chunk k + 1 is pooled.  With C chunks, sample b of the batch belongs to chunk `b // (B / C)` and,
 inside the chunk, to rank `(b % (B / C)) // (B / (C * world))`; a rank's output rows are its samples in
-batch order.
+batch order.  With the other two exchanges rank r ends with samples `[r, r + 1) * B / world`.
+
+Outputs of the peer and copy exchanges are views of buffers the module owns (two, used in turn): a result is
+valid until the call after the next one, and no longer after `close()` or a change of batch size.
 """
 from __future__ import annotations
 
@@ -192,7 +200,8 @@ class ShardedFeatEmbed:
 
     def __init__(self, rank: int, world: int, owner: Sequence[int], dims: Sequence[int],
                  local_tables: Optional[List[torch.Tensor]] = None, device=None, group=None, chunks: int = 4,
-                 pool_fn: Optional[Callable] = None, place_fn: Optional[Callable] = None, exchange: str = "nccl"):
+                 pool_fn: Optional[Callable] = None, place_fn: Optional[Callable] = None, exchange: str = "nccl",
+                 out_dtype: torch.dtype = torch.float32, columns: str = "owner"):
         if len(owner) != len(dims):
             raise ValueError("owner and dims must have one entry per feature")
         self.rank, self.world, self.group = rank, world, group
@@ -226,11 +235,29 @@ class ShardedFeatEmbed:
             self.device = torch.device(device) if device is not None else torch.device("cpu")
         self._segs = {}      # rows per chunk -> device descriptor tensor for the placement kernel
         self._bufs = {}
-        if exchange not in ("nccl", "peer"):
-            raise ValueError("exchange must be 'nccl' or 'peer'")
-        if exchange == "peer" and pool_fn is not None:
-            raise ValueError("the peer exchange exists only on GPUs")
-        self.exchange = exchange
+        if exchange not in ("nccl", "peer", "copy"):
+            raise ValueError("exchange must be 'nccl', 'peer' or 'copy'")
+        if exchange != "nccl" and pool_fn is not None:
+            raise ValueError("the peer and copy exchanges exist only on GPUs")
+        if out_dtype != torch.float32 and exchange == "nccl":
+            raise ValueError("the NCCL exchange carries fp32 rows only")
+        if columns not in ("owner", "canonical"):
+            raise ValueError("columns must be 'owner' or 'canonical'")
+        if columns == "canonical" and out_dtype != torch.float32:
+            raise ValueError("the placement pass restores feature order for fp32 rows only")
+        self.exchange, self.out_dtype, self.columns = exchange, out_dtype, columns
+        if self.local is not None:
+            self.local.set_output_dtype(out_dtype)
+        # copy exchange: rank s's features side by side (increasing feature order) in one block, blocks in rank order
+        self.block_col = [sum(self.units_of[:r]) for r in range(world)]
+        nxt = list(self.block_col)
+        self.owner_major_col = []
+        for f, o in enumerate(self.owner):
+            self.owner_major_col.append(nxt[o])
+            nxt[o] += self.dims[f]
+        # where feature f starts in a row of the result
+        self.column_of = self.owner_major_col if (exchange == "copy" and columns == "owner") else self.col_of
+        self._copy_done = [None, None]
         self._peer = None    # (batch, own pointers, per-buffer pointer lists, output views, mapped peer pointers)
         self._step = 0
 
@@ -276,6 +303,8 @@ class ShardedFeatEmbed:
             batch = self._empty_rank_batch
         if self.exchange == "peer":
             return self._forward_peer(values, offsets, batch)
+        if self.exchange == "copy":
+            return self._forward_copy(values, offsets, batch, out)
         if batch % (W * Cn) != 0:
             raise ValueError(f"batch {batch} must be a multiple of world * chunks = {W * Cn}")
         bc = batch // Cn          # samples per chunk
@@ -331,8 +360,17 @@ class ShardedFeatEmbed:
         W = self.world
         if batch % W or (batch // W) % 32:
             raise ValueError(f"peer exchange needs batch / world to be a multiple of 32 (batch {batch}, world {W})")
+        self._map_result_buffers(batch)
+        if self.local is not None:
+            self.local.set_output_columns([self.col_of[f] for f in self.local_features], self.units)
+
+    def _map_result_buffers(self, batch: int):
+        """Two result matrices [batch / world, units] per rank, allocated by the library and mapped into every
+        other rank's process (CUDA IPC)."""
+        W = self.world
         rows = batch // W
-        nbytes = rows * self.units * 4
+        es = 4 if self.out_dtype == torch.float32 else 2
+        nbytes = rows * self.units * es
         own, handles = [], torch.empty((2, 64), dtype=torch.uint8)
         for b in range(2):
             ptr = C.c_void_p()
@@ -355,17 +393,67 @@ class ShardedFeatEmbed:
                     ptrs[b][r] = int(p.value)
                     mapped.append(int(p.value))
 
+        units = self.units
+        typestr = "<f4" if es == 4 else "<i2"
+
         class _View:  # torch view of a library-owned buffer
             def __init__(self, ptr):
-                self.__cuda_array_interface__ = {"shape": (rows, units), "typestr": "<f4", "data": (ptr, False),
+                self.__cuda_array_interface__ = {"shape": (rows, units), "typestr": typestr, "data": (ptr, False),
                                                  "version": 2}
 
-        units = self.units
         views = [torch.as_tensor(_View(p), device=self.device) for p in own]
-        if self.local is not None:
-            self.local.set_output_columns([self.col_of[f] for f in self.local_features], self.units)
+        if es == 2:
+            views = [v.view(self.out_dtype) for v in views]
         self._flag = torch.zeros(1, dtype=torch.float32, device=self.device)
         self._peer = (batch, own, ptrs, views, mapped)
+
+    # -- exchange through the copy engines -------------------------------------
+    def _forward_copy(self, values, offsets, batch: int, out: Optional[torch.Tensor]) -> torch.Tensor:
+        W, Cn = self.world, self.chunks
+        if batch % (W * Cn) != 0:
+            raise ValueError(f"batch {batch} must be a multiple of world * chunks = {W * Cn}")
+        if self._peer is None or self._peer[0] != batch:
+            self.close()
+            self._map_result_buffers(batch)
+            self._send = [torch.empty((batch, max(self.local_units, 1)), dtype=self.out_dtype, device=self.device)
+                          for _ in range(2)] if self.local is not None else None
+            self._copy_done = [None, None]
+        _, _, ptrs, views, _ = self._peer
+        b = self._step % 2
+        self._step += 1
+        cur = torch.cuda.current_stream(self.device)
+        if self._copy_done[b] is not None:
+            cur.wait_event(self._copy_done[b])  # the copies that read this send buffer two calls ago are done
+        if self.local is not None:
+            self.local.forward_exchange(values, offsets, self._send[b], ptrs[b], self.rank, self.units,
+                                        self.block_col[self.rank], Cn, self._comm)
+        with torch.cuda.stream(self._comm):
+            if self.local is None:
+                self._comm.wait_stream(cur)
+            dist.all_reduce(self._flag, group=self.group)  # after it, every rank's copies into my matrix are complete
+            done = torch.cuda.Event()
+            done.record()
+        self._copy_done[b] = done
+        cur.wait_stream(self._comm)
+        if self.columns == "owner":
+            return views[b]
+        rows = batch // W
+        if out is None:
+            out = torch.empty((rows, self.units), dtype=torch.float32, device=self.device)
+        key = ("copy", rows)
+        segs = self._segs.get(key)
+        if segs is None:
+            import numpy as np
+
+            rec = np.zeros(len(self.dims), dtype=[("src_off", "<i8"), ("src_ld", "<i4"), ("dst_col", "<i4"),
+                                                  ("width", "<i4"), ("pad", "<i4")])
+            for f in range(len(self.dims)):
+                rec[f] = (self.owner_major_col[f], self.units, self.col_of[f], self.dims[f], 0)
+            segs = self._segs[key] = torch.from_numpy(rec.view(np.uint8).copy()).to(self.device)
+        _lib.check(self._lib.eb_place_columns(C.c_void_p(views[b].data_ptr()), C.c_void_p(out.data_ptr()), rows,
+                                              out.stride(0), len(self.dims), C.c_void_p(segs.data_ptr()),
+                                              self.device.index, C.c_void_p(cur.cuda_stream)))
+        return out
 
     def _forward_peer(self, values, offsets, batch: int) -> torch.Tensor:
         if self._peer is None or self._peer[0] != batch:
@@ -380,7 +468,8 @@ class ShardedFeatEmbed:
         return views[b]
 
     def close(self) -> None:
-        """Unmap peers' buffers and free this rank's (call on every rank, after a barrier)."""
+        """Unmap peers' buffers and free this rank's (call on every rank, after a barrier).  Tensors returned by
+        the peer and copy exchanges are views of these buffers and are invalid from here on."""
         if self._peer is not None:
             _, own, _, views, mapped = self._peer
             del views

@@ -284,6 +284,45 @@ def algorithmic_bytes(cfg: ModelConfig, offsets: Sequence[np.ndarray], index_byt
     return total
 
 
+def sampled_cells(cfg: ModelConfig, values: Sequence[np.ndarray], offsets: Sequence[np.ndarray], n: int,
+                  seed: int = 0, features: Optional[Sequence[int]] = None):
+    """`n` random (sample, feature) cells of one batch with what they must pool to: yields
+    (sample, position of the feature in `features`, expected fp32 vector).  The expected vector is the float64 sum
+    of the bag's rows regenerated from the counter-based weights (no table is stored), rounded to fp32; an empty
+    bag gives zeros.  `values` / `offsets` are per-feature lists aligned with `features` (default: all)."""
+    feats = list(range(len(cfg.features))) if features is None else list(features)
+    rng = np.random.default_rng(seed)
+    batch = len(offsets[0]) - 1
+    for _ in range(n):
+        k = int(rng.integers(0, len(feats)))
+        b = int(rng.integers(0, batch))
+        fs = cfg.features[feats[k]]
+        idx = np.asarray(values[k][int(offsets[k][b]):int(offsets[k][b + 1])], dtype=np.int64)
+        if len(idx) == 0:
+            yield b, k, np.zeros(fs.dim, dtype=np.float32)
+            continue
+        uniq, inv = np.unique(idx, return_inverse=True)
+        rows = synth_rows(fs.seed, uniq, fs.dim, fs.dtype).astype(np.float64)
+        yield b, k, rows[inv].sum(axis=0).astype(np.float32)
+
+
+def verify_sampled_cells(out_host: np.ndarray, first_cols: Sequence[int], cfg: ModelConfig, values, offsets, n: int,
+                         seed: int = 0, features: Optional[Sequence[int]] = None) -> dict:
+    """Compare `n` sampled cells of a pooled output (host array [batch, units]; feature k of `features` starts at
+    column first_cols[k]) with sums of regenerated rows.  Returns the cell count, the largest relative error
+    (|got - expect| / max(|expect|, 1e-3)) and whether every sampled empty bag was exactly zero."""
+    feats = list(range(len(cfg.features))) if features is None else list(features)
+    worst, zeros_ok = 0.0, True
+    for b, k, expect in sampled_cells(cfg, values, offsets, n, seed, features):
+        dim = cfg.features[feats[k]].dim
+        got = out_host[b, first_cols[k]:first_cols[k] + dim]
+        if int(offsets[k][b]) == int(offsets[k][b + 1]):
+            zeros_ok = zeros_ok and bool(np.all(got == 0.0))
+        err = np.abs(got.astype(np.float64) - expect) / np.maximum(np.abs(expect), 1e-3)
+        worst = max(worst, float(err.max()))
+    return {"cells": n, "max_rel_err": worst, "empty_bags_exact_zero": zeros_ok}
+
+
 def make_tables_numpy(cfg: ModelConfig) -> List[np.ndarray]:
     """All tables on the host (small configurations only)."""
     return [synth_table(fs.seed, fs.rows, fs.dim, fs.dtype) for fs in cfg.features]

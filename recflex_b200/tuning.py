@@ -28,6 +28,7 @@ from __future__ import annotations
 
 import json
 import math
+import os
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -107,6 +108,16 @@ class TuneResult:
             stats=[InputStats(*s) for s in d.get("stats", [])],
             overlap=int(d.get("overlap", 0)),
         )
+
+    def apply(self, module: FeatEmbed) -> None:
+        """Install the schedules, the occupancy and the kernel-overlap setting on `module`."""
+        module.set_schedules(self.schedules, occupancy=self.occupancy)
+        module.set_kernel_overlap(self.overlap)
+
+
+def tuned_path(workload: str) -> str:
+    """Where the committed tuning result of a benchmark workload ('cfg2', 'cfg3', ...) lives."""
+    return os.path.join(os.path.dirname(os.path.abspath(__file__)), "tuned", f"{workload}.json")
 
 
 def input_stats(offsets: Sequence[torch.Tensor]) -> List[InputStats]:

@@ -45,3 +45,20 @@ def small_model(cfg_id: int, row_scale: float, batch: int, seed: int = 0):
     tables = synth.make_tables_numpy(cfg)
     values, offsets = synth.gen_batch(cfg, seed)
     return cfg, tables, values, offsets
+
+
+def compacted_model(cfg, values):
+    """Tables too large for the host: keep only the rows a batch touches (regenerated from the counter-based
+    weights) and renumber the indices.  Returns (tables, values) for the oracle; offsets stay as they are."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    def one(args):
+        fs, v = args
+        uniq, inv = np.unique(np.asarray(v, dtype=np.int64), return_inverse=True)
+        if len(uniq) == 0:
+            uniq = np.zeros(1, dtype=np.int64)
+        return synth.synth_rows(fs.seed, uniq, fs.dim, fs.dtype), inv.astype(np.int64)
+
+    with ThreadPoolExecutor(max_workers=16) as pool:
+        res = list(pool.map(one, zip(cfg.features, values)))
+    return [r[0] for r in res], [r[1] for r in res]

@@ -87,3 +87,10 @@ def test_sharded_forward_two_gloo_ranks(chunks):
     res = run_workers(2, "gloo", ["--chunks", str(chunks)])
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
     assert "sharded ok gloo world 2" in res.stdout
+
+
+def test_sharded_cfg4_shaped_plan_two_gloo_ranks():
+    """Host logic on the sharded benchmark configuration scaled down (400 features, the benchmark's planner call)."""
+    res = run_workers(2, "gloo", ["--model", "cfg4", "--chunks", "2", "--batch", "24"])
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
+    assert "sharded ok gloo world 2" in res.stdout

@@ -63,3 +63,59 @@ def test_noalloc_refuses_more_features_than_its_array_holds(lib):
     rc = _call_noalloc(lib, [t] * F, vals, offs, out)
     assert rc == _lib.EB_ERR_TOO_LARGE
     assert b"exceed" in lib.eb_last_error()
+
+
+def test_noalloc_status_word_and_capture_refusal(lib):
+    cfg, tables, values, offsets = small_model(1, 0.1, 256)
+    tables_dev = device_tables(tables)
+    pv, po = synth.pack_batch(values, offsets)
+    dv, do = torch.from_numpy(pv).cuda(), torch.from_numpy(po).cuda()
+    out = torch.empty((256, sum(t.shape[1] for t in tables)), device="cuda:0")
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    _lib.check(_call_noalloc(lib, tables_dev, dv, do, out))
+    assert lib.eb_noalloc_check_status(0, stream) == _lib.EB_OK
+    bad = dv.clone()
+    bad[3] = tables[0].shape[0] + 7  # an index past the first table's last row: skipped, and reported
+    _lib.check(_call_noalloc(lib, tables_dev, bad, do, out))
+    assert lib.eb_noalloc_check_status(0, stream) == _lib.EB_ERR_BAD_INPUT
+    _lib.check(_call_noalloc(lib, tables_dev, dv, do, out))  # the next call starts from a clean status word
+    assert lib.eb_noalloc_check_status(0, stream) == _lib.EB_OK
+    # a call stages its descriptors through host memory that the next call overwrites: refused under capture
+    graph = torch.cuda.CUDAGraph()
+    scratch = torch.zeros(8, device="cuda:0")
+    with torch.cuda.graph(graph):
+        scratch.add_(1.0)
+        rc = _call_noalloc(lib, tables_dev, dv, do, out)
+    assert rc == _lib.EB_ERR_UNSUPPORTED and b"captured" in lib.eb_last_error()
+
+
+def test_noalloc_two_host_threads_take_turns(lib):
+    """Two host threads call the entry point on one GPU and one stream, each with its own model: the calls are
+    serialised on the host (a per-device lock around staging, upload and launches) and run in order on the GPU."""
+    import threading
+
+    models = []
+    for cfg_id, scale, batch in ((1, 0.1, 256), (2, 0.01, 300)):
+        cfg, tables, values, offsets = small_model(cfg_id, scale, batch)
+        pv, po = synth.pack_batch(values, offsets)
+        models.append((tables, values, offsets, device_tables(tables), torch.from_numpy(pv).cuda(),
+                       torch.from_numpy(po).cuda()))
+    errors = []
+
+    def worker(k):
+        try:
+            tables, values, offsets, tdev, dv, do = models[k]
+            for _ in range(20):
+                out = torch.full((do.shape[1] - 1, sum(t.shape[1] for t in tables)), float("nan"), device="cuda:0")
+                _lib.check(_call_noalloc(lib, tdev, dv, do, out))
+                torch.cuda.synchronize()
+                check_against_oracle(out, tables, values, offsets, "f32")
+        except Exception as e:  # noqa: BLE001 - reported by the main thread
+            errors.append(repr(e))
+
+    threads = [threading.Thread(target=worker, args=(k,)) for k in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
