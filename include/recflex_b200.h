@@ -211,8 +211,8 @@ int eb_forward_timed(eb_handle* h, int64_t batch, const void* const* values_ptrs
 
 /*
  * Kernel timing.  eb_kernel_timing(h, 1) makes every later forward record a
- * CUDA event pair around its fused-kernel launch (a ring of 256 pairs; the
- * binding kernel is outside the pair).  eb_kernel_times() waits for the
+ * CUDA event pair around its kernels: the binding kernel, the warp-per-bag
+ * kernel when a feature uses it, and the fused kernel (a ring of 256 pairs).  eb_kernel_times() waits for the
  * recorded pairs, writes the elapsed milliseconds of each launch since the
  * previous read (oldest first, at most `cap`) and clears the ring.  This is the
  * in-process counterpart of the reference's global-stage measurement, the
@@ -229,6 +229,16 @@ int eb_kernel_times(eb_handle* h, float* ms, int cap, int* count);
  * Synchronises `stream`.  The reference performs no such check.
  */
 int eb_check_status(eb_handle* h, void* workspace, void* stream);
+
+/*
+ * The run-time binding of the last forward that used `workspace`: how many bags
+ * the device bound to one warp tile, per feature (HOST array of num_features
+ * entries; ceil(batch / bags_per_tile[f]) is the feature's tile count).
+ * Synchronises `stream`.  The counterpart of reading the per-batch block counts
+ * of the reference's host preprocess (RecFlex/tuning/measure.py measure_task_blocks,
+ * used by Tuner.tune_fixed_thread_binding, RecFlex/tuning/tuner.py:312-357).
+ */
+int eb_last_binding(eb_handle* h, void* workspace, void* stream, int32_t* bags_per_tile);
 
 /*
  * Fill a table with the library's counter-based synthetic weights: element
@@ -268,6 +278,24 @@ int eb_forward_peers(eb_handle* h, int64_t batch, const void* const* values_ptrs
                      const void* const* offsets_ptrs, const int64_t* nnz, int index_dtype,
                      int offsets_have_end, float* const* peer_out, int world, int64_t out_ld,
                      void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Bags far longer than the rest.  A bag whose rows add up to `min_bytes` or
+ * more (default 1 MB; 0 switches the mechanism off) is not pooled by the warp
+ * that meets it, where it would be the kernel's tail: the EB_SCHED_STREAM /
+ * EB_SCHED_PIPE walk hands it to a second kernel launched right after the fused
+ * one, in which many warps pool segments of the bag and the warp that finishes
+ * the last segment adds the partial sums in segment order (no atomics on the
+ * data, the same bits on every run).  This is the library's block-per-bag
+ * schedule; it replaces mbs::SparseSegmentReduceCore
+ * (examples/csrc/include/multi_block_per_sample_kernel.cuh:17-112), which adds
+ * its tiles with atomicAdd into an output it never zeroes.  At most 256 bags
+ * per call are handed over (further ones are pooled in place); batches with
+ * 64-bit indices, rows wider than 512 bytes, the chunked order of
+ * eb_forward_exchange and eb_forward_packed_noalloc pool every bag in place.
+ * The second kernel costs a few microseconds per call when no bag is long.
+ */
+int eb_set_long_bag_split(eb_handle* h, int64_t min_bytes);
 
 /*
  * Element type of the pooled output (no counterpart in the reference, whose

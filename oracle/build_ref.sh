@@ -3,10 +3,11 @@
 # RecFlex checkout, compiling the reference's sources where they lie:
 #   libref_kernels.so  the reference's device templates behind oracle/ref_kernels.cu (sm_100a)
 #   libref_host.so     the reference's host text parsers behind oracle/ref_host_shim.cc
-# Usage: oracle/build_ref.sh [path to the RecFlex checkout; default: $RECFLEX_REF, else the build container's mount]
+# Usage: oracle/build_ref.sh <path to the RecFlex checkout>   (or set $RECFLEX_REF)
 set -euo pipefail
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
-REF="${1:-${RECFLEX_REF:-/root/reference}}"
+REF="${1:-${RECFLEX_REF:-}}"
+[ -n "$REF" ] || { echo "usage: $0 <path to the RecFlex checkout> (or set RECFLEX_REF)" >&2; exit 2; }
 OUT="$HERE/_ref"
 [ -d "$REF/examples/csrc/include" ] || { echo "no RecFlex checkout at $REF" >&2; exit 1; }
 mkdir -p "$OUT"

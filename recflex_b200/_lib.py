@@ -71,6 +71,7 @@ PROTOTYPES = {
     "eb_kernel_timing": (C.c_int, [C.c_void_p, C.c_int]),
     "eb_kernel_times": (C.c_int, [C.c_void_p, C.POINTER(C.c_float), C.c_int, C.POINTER(C.c_int)]),
     "eb_check_status": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
+    "eb_last_binding": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]),
     "eb_fill_table": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_uint64, C.c_float, C.c_int,
                                 C.c_void_p]),
     "eb_set_output_columns": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_int64]),
@@ -93,6 +94,7 @@ PROTOTYPES = {
                                             C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_void_p]),
     "eb_noalloc_check_status": (C.c_int, [C.c_int, C.c_void_p]),
     "eb_set_output_dtype": (C.c_int, [C.c_void_p, C.c_int]),
+    "eb_set_long_bag_split": (C.c_int, [C.c_void_p, C.c_int64]),
     "eb_forward_exchange": (C.c_int, [C.c_void_p, C.c_int64, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
                                       C.POINTER(C.c_int64), C.c_int, C.c_int, C.c_void_p, C.c_int64,
                                       C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int,

@@ -58,6 +58,7 @@ def _units():
         ("eb_launch.o", "eb_launch.cu", []),
         ("eb_noalloc.o", "eb_noalloc.cu", []),
         ("eb_warp.o", "eb_warp_inst.cu", []),
+        ("eb_longbag.o", "eb_longbag_inst.cu", []),
     ]
     for occ in range(1, 9):
         units.append((f"eb_fused_occ{occ}.o", "eb_fused_inst.cu", [f"-DEB_OCC={occ}"]))

@@ -176,6 +176,11 @@ __global__ void __launch_bounds__(kBindThreads) eb_bind_kernel(LaunchArgs a, int
   }
   if (tid < kMaxPeers) hdr->peer_out[tid] = a.peer_out[tid];
   if (tid < kMaxChunks) reinterpret_cast<ChunkSync*>(a.ws + L.chunk_sync)->done[tid] = 0u;
+  if (a.long_bytes > 0) {
+    LongBagList* ll = reinterpret_cast<LongBagList*>(a.ws + L.long_list);
+    if (tid < kMaxLongBags) ll->done[tid] = 0u;
+    if (tid == 0) { ll->count = 0u; ll->seg_ticket = 0u; }
+  }
 }
 
 // Sets every chunk flag to the call's epoch.  Launched right after the fused kernel in chunked order, so that a

@@ -94,6 +94,8 @@ struct eb_handle {
   std::vector<cudaEvent_t> t0, t1;
   int t_count = 0;
   int out_dtype = EB_OUT_F32;  // element type of the output matrix
+  int only_kind = 0, only_unroll = 0;   // the one schedule (and unroll) every fused-kernel feature uses, 0 = mixed
+  int64_t long_bag_bytes = 1 << 20;     // bags gathering at least this much are pooled by eb_longbag_kernel (0 = off)
   uint32_t epoch = 0;          // calls in chunked ticket order so far (eb_forward_exchange)
 };
 
@@ -181,6 +183,7 @@ LaunchArgs make_args(const eb_handle* h, int64_t batch, int index_dtype, int has
   a.out_vec = out_vec_of(out, out_ld, out_elem_bytes(h));
   a.warps_total = h->sm_count * h->occupancy * kWarpsPerCta;
   a.ring_bytes = (int32_t)(h->smem_bytes / kWarpsPerCta);
+  a.long_bytes = h->long_bag_bytes;
   return a;
 }
 
@@ -196,20 +199,23 @@ int run(eb_handle* h, const LaunchArgs& a_in, bool timing, cudaStream_t st) {
                        a.chunks == 0;  // chunked order: the warp-per-bag kernel must be done before any chunk is published
   const int ctas_per_sm = overlap && h->overlap_ctas < h->occupancy ? h->overlap_ctas : h->occupancy;
   a.warps_total = h->sm_count * ctas_per_sm * kWarpsPerCta;
-  EB_CUDA(launch_bind(a, timing, st));
   const bool rec = h->time_kernels && h->t_count < kTimeRing;
   if (rec) EB_CUDA(cudaEventRecord(h->t0[h->t_count], st));
+  EB_CUDA(launch_bind(a, timing, st));
   if (overlap) {
     EB_CUDA(cudaEventRecord(h->fork_ev, st));
-    EB_CUDA(launch_fused(a, h->occupancy, timing, h->sm_count * ctas_per_sm, h->smem_bytes, st));
+    EB_CUDA(launch_fused(a, h->occupancy, timing, h->sm_count * ctas_per_sm, h->smem_bytes, st, h->only_kind,
+                         h->only_unroll));
     EB_CUDA(cudaStreamWaitEvent(h->side, h->fork_ev, 0));
     EB_CUDA(launch_warp(a, timing, h->warp_features, h->side));
     EB_CUDA(cudaEventRecord(h->join_ev, h->side));
     EB_CUDA(cudaStreamWaitEvent(st, h->join_ev, 0));
   } else {
     if (h->warp_features) EB_CUDA(launch_warp(a, timing, h->warp_features, st));
-    EB_CUDA(launch_fused(a, h->occupancy, timing, h->sm_count * ctas_per_sm, h->smem_bytes, st));
+    EB_CUDA(launch_fused(a, h->occupancy, timing, h->sm_count * ctas_per_sm, h->smem_bytes, st, h->only_kind,
+                         h->only_unroll));
   }
+  if (a.long_bytes > 0) EB_CUDA(launch_longbag(a, timing, h->sm_count, st));
   if (a.chunks > 0) EB_CUDA(launch_release(a, st));
   if (rec) {
     EB_CUDA(cudaEventRecord(h->t1[h->t_count], st));
@@ -357,8 +363,8 @@ int eb_set_schedules(eb_handle* h, const eb_schedule* per_feature, int occupancy
       const int rc = check_schedule(per_feature[f], f);
       if (rc != EB_OK) return rc;
     }
-    // deepest ring any pipelined feature needs: unroll 2 -> 2 x 4 cells, 4 -> 4 x 3, 8 -> 8 x 2; never fewer than
-    // 12, because batches with 64-bit indices always run the unroll-4 / 3-stage variant whatever was requested
+    // deepest ring any pipelined feature needs (pipe_cells: never fewer than the unroll-4 variant's, because batches
+    // with 64-bit indices always run that variant whatever was requested)
     int cells = 0;
     for (int f = 0; f < h->num_features; ++f) {
       h->sched[f] = resolve(per_feature[f]);
@@ -366,8 +372,7 @@ int eb_set_schedules(eb_handle* h, const eb_schedule* per_feature, int occupancy
       if (h->sched[f].kind == EB_SCHED_PIPE && !h->feats[f].vec) h->sched[f].kind = EB_SCHED_STREAM;
       apply_schedule(h->feats[f], h->sched[f]);
       if (h->sched[f].kind == EB_SCHED_PIPE) {
-        const int u = h->sched[f].unroll;
-        const int need = u == 8 ? 16 : 12;
+        const int need = pipe_cells(h->sched[f].unroll);
         cells = need > cells ? need : cells;
       }
     }
@@ -375,6 +380,18 @@ int eb_set_schedules(eb_handle* h, const eb_schedule* per_feature, int occupancy
     h->warp_features = 0;
     for (int f = 0; f < h->num_features; ++f)
       h->warp_features += (h->feats[f].kind == EB_SCHED_WARP && h->feats[f].vec) ? 1 : 0;
+    // do all features the fused kernel pools by vector rows agree on a stream / pipe schedule (and on its unroll)?
+    int kind = -1, unroll = -1;
+    for (int f = 0; f < h->num_features; ++f) {
+      const FeatStatic& fs = h->feats[f];
+      if (!fs.vec || fs.kind == EB_SCHED_WARP) continue;  // element-wise fallback / the warp-per-bag kernel's
+      const int u = (fs.kind == EB_SCHED_PIPE && fs.unroll < 2) ? 2 : fs.unroll;
+      kind = kind == -1 ? fs.kind : (kind == fs.kind ? kind : 0);
+      unroll = unroll == -1 ? u : (unroll == u ? unroll : 0);
+    }
+    const bool family = kind == EB_SCHED_STREAM || kind == EB_SCHED_PIPE;
+    h->only_kind = family ? kind : 0;
+    h->only_unroll = (family && (unroll == 2 || unroll == 4 || unroll == 8)) ? unroll : 0;
     DeviceGuard guard(h->device);
     const int rc = upload_feats(h);
     if (rc != EB_OK) return rc;
@@ -421,7 +438,7 @@ int eb_max_concurrent_ctas(const eb_handle* h, int occupancy, int* ctas) {
   const int occ = occupancy ? occupancy : h->occupancy;
   DeviceGuard guard(h->device);
   int per_sm = 0;
-  EB_CUDA(fused_ctas_per_sm(occ, h->smem_bytes, &per_sm));
+  EB_CUDA(fused_ctas_per_sm(occ, h->smem_bytes, &per_sm, h->only_kind, h->only_unroll));
   *ctas = h->sm_count * (per_sm < occ ? per_sm : occ);
   return EB_OK;
 }
@@ -469,6 +486,13 @@ int eb_forward_peers(eb_handle* h, int64_t batch, const void* const* values_ptrs
   a.peer_spread = h->peer_interleave ? world : 0;
   for (int r = 0; r < world; ++r) a.peer_out[r] = peer_out[r];
   return run(h, a, false, st);
+}
+
+int eb_set_long_bag_split(eb_handle* h, int64_t min_bytes) {
+  if (!h) return fail(EB_ERR_INVALID_ARG, "null handle");
+  if (min_bytes < 0) return fail(EB_ERR_INVALID_ARG, "negative size");
+  h->long_bag_bytes = min_bytes;
+  return EB_OK;
 }
 
 int eb_set_output_dtype(eb_handle* h, int out_dtype) {
@@ -727,6 +751,17 @@ int eb_check_status(eb_handle* h, void* workspace, void* stream) {
                 (hdr.status & kStatusBadOffsets) ? "; offsets were not a non-decreasing sequence inside [0, nnz]" : "");
   if (hdr.status & kStatusBadOffsets)
     return fail(EB_ERR_BAD_INPUT, "offsets were not a non-decreasing sequence inside [0, nnz]; they were clamped");
+  return EB_OK;
+}
+
+int eb_last_binding(eb_handle* h, void* workspace, void* stream, int32_t* bags_per_tile) {
+  if (!h || !workspace || !bags_per_tile) return fail(EB_ERR_INVALID_ARG, "null argument");
+  DeviceGuard guard(h->device);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const WsLayout L = ws_layout(h->num_features);
+  EB_CUDA(cudaMemcpyAsync(bags_per_tile, static_cast<char*>(workspace) + L.bags_per_tile,
+                          sizeof(int32_t) * h->num_features, cudaMemcpyDeviceToHost, st));
+  EB_CUDA(cudaStreamSynchronize(st));
   return EB_OK;
 }
 

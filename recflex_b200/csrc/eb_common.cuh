@@ -14,6 +14,21 @@ constexpr int kMaxOccupancy = 8;        // 2048 threads per SM / 256
 constexpr int kBindThreads = 1024;
 constexpr int kPipeCellBytes = 512;      // one ring cell: 32 lanes x 16 bytes
 constexpr int kPipeMaxCells = 16;        // unroll x stages of the deepest pipelined variant
+#ifndef EB_PIPE_D2
+#define EB_PIPE_D2 4
+#define EB_PIPE_D4 3
+#define EB_PIPE_D8 2
+#endif
+// Macro-steps the pipelined schedule keeps in flight, by unroll (rows per macro-step); the ring holds unroll x depth
+// cells of 512 bytes per warp.  Batches with 64-bit indices always run the unroll-4 variant.
+__host__ __device__ constexpr inline int pipe_depth(int unroll) {
+  return unroll <= 2 ? EB_PIPE_D2 : (unroll == 4 ? EB_PIPE_D4 : EB_PIPE_D8);
+}
+__host__ __device__ constexpr inline int pipe_cells(int unroll) {
+  const int u = unroll <= 2 ? 2 : (unroll == 4 ? 4 : 8);
+  const int own = u * pipe_depth(u), i64 = 4 * pipe_depth(4);
+  return own > i64 ? own : i64;
+}
 constexpr int kMaxLptFeatures = 2048;   // features beyond this keep their input order
 
 // status bits written by the kernels (never a trap)
@@ -72,9 +87,35 @@ struct __align__(128) ChunkSync {
 };
 static_assert(sizeof(ChunkSync) == 512, "ChunkSync must stay 512 bytes");
 
-// Host/device view of where each array sits inside the workspace.
+// Long bags: a bag whose rows add up to LaunchArgs::long_bytes or more is not pooled by the warp that meets it
+// (it would be that warp's, and the kernel's, tail); the warp appends it to this list and eb_longbag_kernel, launched
+// after the fused kernel, pools every listed bag with many warps: the bag is cut into segments, every segment's
+// partial sum goes to `long_pool`, and the warp that finishes a bag's last segment adds the partials in segment
+// order (no atomics on the data, same result on every run).  A full list simply stops accepting bags.
+constexpr int kMaxLongBags = 256;
+constexpr int kMaxLongSegments = 128;          // per bag
+constexpr int kLongPoolFloats = 256 * 1024;    // 1 MB of partial sums
+
+struct __align__(16) LongBag {
+  int32_t feat;
+  int32_t pad_;
+  int64_t bag;     // position in the batch
+  int64_t begin;   // entries [begin, end) of the feature's index list, already validated
+  int64_t end;
+};
+
+struct __align__(128) LongBagList {
+  uint32_t count;        // bags appended (may exceed kMaxLongBags: the excess was pooled in place)
+  uint32_t seg_ticket;   // next segment to pool
+  uint32_t pad_[30];
+  uint32_t done[kMaxLongBags];  // finished segments per bag
+  LongBag item[kMaxLongBags];
+};
+
+// Host/device view of where each array sits inside the workspace.  The long-bag sections come last: a caller that
+// keeps long-bag splitting off (long_bytes == 0) may pass a workspace that ends at `long_list`.
 struct WsLayout {
-  size_t header, tile_prefix, cta_prefix, order, bags_per_tile, dyn, feat_ns, chunk_sync, total;
+  size_t header, tile_prefix, cta_prefix, order, bags_per_tile, dyn, feat_ns, chunk_sync, long_list, long_pool, total;
 };
 
 __host__ __device__ constexpr inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -90,6 +131,8 @@ __host__ __device__ constexpr inline WsLayout ws_layout(int F) {
   l.dyn = o;           o = align_up(o + sizeof(FeatDyn) * (size_t)F, 128);
   l.feat_ns = o;       o = align_up(o + sizeof(unsigned long long) * (size_t)F, 128);
   l.chunk_sync = o;    o += sizeof(ChunkSync);
+  l.long_list = o;     o += sizeof(LongBagList);
+  l.long_pool = o;     o += sizeof(float) * (size_t)kLongPoolFloats;
   l.total = o;
   return l;
 }
@@ -112,6 +155,7 @@ struct LaunchArgs {
   int32_t warps_total;    // persistent warps of the fused kernel (for tile sizing)
   int32_t ring_bytes;     // shared memory per warp for the pipelined schedule's ring (0 when no feature uses it)
   int32_t peer_spread;    // peer mode: number of ranks to deal a feature's consecutive tiles over (0 = batch order)
+  int64_t long_bytes;     // bags that gather at least this many bytes go to eb_longbag_kernel (0 = pooled in place)
   // chunked ticket order (chunks > 0; for exchanges that ship finished chunks while later ones are pooled): the
   // batch is seen as `world` runs of dest_rows bags (one per destination rank), each cut into `chunks` pieces of
   // chunk_rows bags; the tickets cover piece 0 of every run for every feature, then piece 1, ...  A tile never

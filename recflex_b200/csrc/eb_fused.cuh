@@ -28,37 +28,40 @@ namespace ebk {
     EB_DISPATCH_UNROLL(FN, float, 4, I64)                          \
   }
 
-// EB_SCHED_STREAM: the register walk
-#define EB_DISPATCH_STREAM_T(T, V, I64)                                        \
-  switch (fs.unroll) {                                                         \
-    case 1: tile_stream<T, V, 1, I64>(ctx, b0, b1, lane, items); break;        \
-    case 2: tile_stream<T, V, 2, I64>(ctx, b0, b1, lane, items); break;        \
-    case 4: tile_stream<T, V, 4, I64>(ctx, b0, b1, lane, items); break;        \
-    default: tile_stream<T, V, 8, I64>(ctx, b0, b1, lane, items); break;       \
+// EB_SCHED_STREAM: the register walk.  FS: fp32 output aligned for the widest store (see walk_store).
+#define EB_DISPATCH_STREAM_T(T, V, I64, FS)                                           \
+  switch (fs.unroll) {                                                                \
+    case 1: tile_stream<T, V, 1, I64, 0, FS>(ctx, b0, b1, lane, items); break;        \
+    case 2: tile_stream<T, V, 2, I64, 0, FS>(ctx, b0, b1, lane, items); break;        \
+    case 4: tile_stream<T, V, 4, I64, 0, FS>(ctx, b0, b1, lane, items); break;        \
+    default: tile_stream<T, V, 8, I64, 0, FS>(ctx, b0, b1, lane, items); break;       \
   }
 
 #define EB_DISPATCH_STREAM(I64)                                    \
   if (fs.dtype == 1) {                                             \
-    EB_DISPATCH_STREAM_T(__half, 8, I64)                           \
+    if (ctx.out_dt == 0 && ctx.out_vec == 2) { EB_DISPATCH_STREAM_T(__half, 8, I64, true) } \
+    else { EB_DISPATCH_STREAM_T(__half, 8, I64, false) }           \
   } else {                                                         \
-    EB_DISPATCH_STREAM_T(float, 4, I64)                            \
+    if (ctx.out_dt == 0 && ctx.out_vec >= 1) { EB_DISPATCH_STREAM_T(float, 4, I64, true) } \
+    else { EB_DISPATCH_STREAM_T(float, 4, I64, false) }            \
   }
 
-// EB_SCHED_PIPE: ring depth is tied to the unroll so that a CTA needs 32 to 64 KB
-// of shared memory: unroll 2 -> 4 stages, 4 -> 3 stages, 8 -> 2 stages.
-#define EB_DISPATCH_PIPE_T(T, V, I64)                                                  \
-  switch (fs.unroll) {                                                                 \
-    case 1:                                                                            \
-    case 2: tile_stream<T, V, 2, I64, 4>(ctx, b0, b1, lane, items, ring); break;       \
-    case 4: tile_stream<T, V, 4, I64, 3>(ctx, b0, b1, lane, items, ring); break;       \
-    default: tile_stream<T, V, 8, I64, 2>(ctx, b0, b1, lane, items, ring); break;      \
+// EB_SCHED_PIPE: ring depth is tied to the unroll (pipe_depth, eb_common.cuh).
+#define EB_DISPATCH_PIPE_T(T, V, I64, FS)                                                              \
+  switch (fs.unroll) {                                                                                 \
+    case 1:                                                                                            \
+    case 2: tile_stream<T, V, 2, I64, pipe_depth(2), FS>(ctx, b0, b1, lane, items, ring); break;       \
+    case 4: tile_stream<T, V, 4, I64, pipe_depth(4), FS>(ctx, b0, b1, lane, items, ring); break;       \
+    default: tile_stream<T, V, 8, I64, pipe_depth(8), FS>(ctx, b0, b1, lane, items, ring); break;      \
   }
 
 #define EB_DISPATCH_PIPE(I64)                                      \
   if (fs.dtype == 1) {                                             \
-    EB_DISPATCH_PIPE_T(__half, 8, I64)                             \
+    if (ctx.out_dt == 0 && ctx.out_vec == 2) { EB_DISPATCH_PIPE_T(__half, 8, I64, true) } \
+    else { EB_DISPATCH_PIPE_T(__half, 8, I64, false) }             \
   } else {                                                         \
-    EB_DISPATCH_PIPE_T(float, 4, I64)                              \
+    if (ctx.out_dt == 0 && ctx.out_vec >= 1) { EB_DISPATCH_PIPE_T(float, 4, I64, true) } \
+    else { EB_DISPATCH_PIPE_T(float, 4, I64, false) }              \
   }
 
 // 64-bit indices are the uncommon case: every schedule kind is instantiated for
@@ -79,8 +82,8 @@ namespace ebk {
     if (fs.dtype == 1) tile_stream<__half, 8, 4, true>(ctx, b0, b1, lane, items); \
     else tile_stream<float, 4, 4, true>(ctx, b0, b1, lane, items); \
   } else {                                                         \
-    if (fs.dtype == 1) tile_stream<__half, 8, 4, true, 3>(ctx, b0, b1, lane, items, ring); \
-    else tile_stream<float, 4, 4, true, 3>(ctx, b0, b1, lane, items, ring); \
+    if (fs.dtype == 1) tile_stream<__half, 8, 4, true, pipe_depth(4)>(ctx, b0, b1, lane, items, ring); \
+    else tile_stream<float, 4, 4, true, pipe_depth(4)>(ctx, b0, b1, lane, items, ring); \
   }
 
 #define EB_DISPATCH_KIND(I64)                                      \
@@ -97,7 +100,24 @@ namespace ebk {
     EB_DISPATCH_PIPE(I64)                                          \
   }
 
-template <int OCC, bool TIMING>
+// One schedule at one unroll, both table dtypes, with and without the fast store.
+#define EB_ONE_WALK(U, D)                                                                              \
+  if (fs.dtype == 1) {                                                                                 \
+    if (ctx.out_dt == 0 && ctx.out_vec == 2) tile_stream<__half, 8, U, false, D, true>(ctx, b0, b1, lane, items, ring);  \
+    else tile_stream<__half, 8, U, false, D, false>(ctx, b0, b1, lane, items, ring);                   \
+  } else {                                                                                             \
+    if (ctx.out_dt == 0 && ctx.out_vec >= 1) tile_stream<float, 4, U, false, D, true>(ctx, b0, b1, lane, items, ring);   \
+    else tile_stream<float, 4, U, false, D, false>(ctx, b0, b1, lane, items, ring);                    \
+  }
+
+// KIND / UNROLL select what the kernel holds.  0 / 0: every schedule at every unroll (any assignment, any index
+// width).  KIND = EB_SCHED_STREAM (4) or EB_SCHED_PIPE (5): only that schedule (plus the element-wise fallback), at
+// every unroll (UNROLL = 0) or at one; for batches with 32-bit indices whose features all agree on it.  What the
+// reference reaches by generating and compiling one kernel per schedule assignment
+// (RecFlex/code_emitter/codegen.py:233-262: only the schedules in use are emitted), these instantiations reach for
+// the assignments that matter most: the register allocation and the instruction-cache footprint are those of the
+// schedule in use, not of the largest one in the library.
+template <int OCC, bool TIMING, int KIND = 0, int UNROLL = 0>
 __global__ void __launch_bounds__(kCtaThreads, OCC) eb_fused_kernel(LaunchArgs a) {
   const int lane = threadIdx.x & 31;
   const int F = a.num_features;
@@ -167,6 +187,9 @@ __global__ void __launch_bounds__(kCtaThreads, OCC) eb_fused_kernel(LaunchArgs a
     ctx.rows_per_peer = a.rows_per_peer;
     ctx.col_off = fs.col_off;
     ctx.status = &hdr->status;
+    ctx.long_list = reinterpret_cast<LongBagList*>(a.ws + L.long_list);
+    ctx.long_bytes = a.chunks > 0 ? 0 : a.long_bytes;  // in chunked order a chunk is complete when its tiles are
+    ctx.feat = f;
     ctx.dim = fs.dim;
     ctx.row_bytes = fs.row_bytes;
     ctx.lg_group = fs.lg_group;
@@ -178,10 +201,25 @@ __global__ void __launch_bounds__(kCtaThreads, OCC) eb_fused_kernel(LaunchArgs a
     long long c0 = 0;
     if (TIMING) c0 = clock64();
 
-    if (a.idx64) {
-      EB_DISPATCH_KIND64()
+    if constexpr (KIND == 0) {
+      if (a.idx64) {
+        EB_DISPATCH_KIND64()
+      } else {
+        EB_DISPATCH_KIND(false)
+      }
     } else {
-      EB_DISPATCH_KIND(false)
+      if (!fs.vec) {
+        if (fs.dtype == 1) tile_warp<__half, 1, 4, false>(ctx, b0, b1, lane);
+        else tile_warp<float, 1, 4, false>(ctx, b0, b1, lane);
+      } else if constexpr (KIND == 5 && UNROLL == 0) {
+        EB_DISPATCH_PIPE(false)
+      } else if constexpr (KIND == 5) {
+        EB_ONE_WALK(UNROLL, pipe_depth(UNROLL))
+      } else if constexpr (UNROLL == 0) {
+        EB_DISPATCH_STREAM(false)
+      } else {
+        EB_ONE_WALK(UNROLL, 0)
+      }
     }
 
     if (TIMING) {
@@ -206,6 +244,7 @@ __global__ void __launch_bounds__(kCtaThreads, OCC) eb_fused_kernel(LaunchArgs a
   }
 }
 
+#undef EB_ONE_WALK
 #undef EB_DISPATCH_UNROLL
 #undef EB_DISPATCH_DTYPE
 #undef EB_DISPATCH_KIND

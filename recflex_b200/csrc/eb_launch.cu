@@ -1,22 +1,24 @@
 // Launchers: pick the fused-kernel instantiation for an occupancy, launch the
 // binding kernel and the table-fill kernel.
-#include <atomic>
+#include <mutex>
+#include <set>
+#include <utility>
 
 #include "eb_bind.cuh"
 #include "eb_launch.h"
 
 namespace ebk {
 
-static FusedKernel pick(int occ, bool timing) {
+static FusedKernel pick(int occ, bool timing, int kind, int unroll) {
   switch (occ) {
-    case 1: return fused_kernel_occ1(timing);
-    case 2: return fused_kernel_occ2(timing);
-    case 3: return fused_kernel_occ3(timing);
-    case 4: return fused_kernel_occ4(timing);
-    case 5: return fused_kernel_occ5(timing);
-    case 6: return fused_kernel_occ6(timing);
-    case 7: return fused_kernel_occ7(timing);
-    default: return fused_kernel_occ8(timing);
+    case 1: return fused_kernel_occ1(timing, kind, unroll);
+    case 2: return fused_kernel_occ2(timing, kind, unroll);
+    case 3: return fused_kernel_occ3(timing, kind, unroll);
+    case 4: return fused_kernel_occ4(timing, kind, unroll);
+    case 5: return fused_kernel_occ5(timing, kind, unroll);
+    case 6: return fused_kernel_occ6(timing, kind, unroll);
+    case 7: return fused_kernel_occ7(timing, kind, unroll);
+    default: return fused_kernel_occ8(timing, kind, unroll);
   }
 }
 
@@ -31,20 +33,21 @@ cudaError_t launch_release(const LaunchArgs& a, cudaStream_t st) {
   return cudaGetLastError();
 }
 
-// Dynamic shared memory above 48 KB must be opted into once per kernel function and device.  The attribute call
-// is cheap and idempotent, so devices beyond the remembered range simply repeat it on every launch.
-static cudaError_t allow_smem(FusedKernel k, int occupancy, bool timing, size_t smem_bytes) {
-  constexpr int kRemembered = 64;
-  static std::atomic<bool> done[kRemembered][kMaxOccupancy + 1][2];
-  if (smem_bytes <= 48 * 1024) return cudaSuccess;
+// Dynamic shared memory above 48 KB (static shared memory counts too) must be opted into once per kernel function
+// and device.
+static cudaError_t allow_smem(FusedKernel k, size_t smem_bytes) {
+  static std::mutex mu;
+  static std::set<std::pair<int, const void*>> done;
+  if (smem_bytes <= 32 * 1024) return cudaSuccess;
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
-  const bool remember = dev >= 0 && dev < kRemembered;
-  if (remember && done[dev][occupancy][timing ? 1 : 0].load(std::memory_order_acquire)) return cudaSuccess;
+  const std::pair<int, const void*> key(dev, reinterpret_cast<const void*>(k));
+  std::lock_guard<std::mutex> lock(mu);
+  if (done.count(key)) return cudaSuccess;
   e = cudaFuncSetAttribute(reinterpret_cast<const void*>(k), cudaFuncAttributeMaxDynamicSharedMemorySize,
                            kPipeMaxCells * kPipeCellBytes * kWarpsPerCta);
-  if (e == cudaSuccess && remember) done[dev][occupancy][timing ? 1 : 0].store(true, std::memory_order_release);
+  if (e == cudaSuccess) done.insert(key);
   return e;
 }
 
@@ -58,17 +61,19 @@ static int helper_grid(int64_t wanted, int ctas_per_sm) {
   return (int)(wanted < 1 ? 1 : (wanted > cap ? cap : wanted));
 }
 
-cudaError_t launch_fused(const LaunchArgs& a, int occupancy, bool timing, int grid, size_t smem_bytes, cudaStream_t st) {
-  FusedKernel k = pick(occupancy, timing);
-  cudaError_t e = allow_smem(k, occupancy, timing, smem_bytes);
+cudaError_t launch_fused(const LaunchArgs& a, int occupancy, bool timing, int grid, size_t smem_bytes, cudaStream_t st,
+                         int kind, int unroll) {
+  if (a.idx64 || timing) kind = unroll = 0;  // the specialised instantiations read 32-bit indices and keep no clocks
+  FusedKernel k = pick(occupancy, timing, kind, unroll);
+  cudaError_t e = allow_smem(k, smem_bytes);
   if (e != cudaSuccess) return e;
   void* params[] = {const_cast<LaunchArgs*>(&a)};
   return cudaLaunchKernel(reinterpret_cast<const void*>(k), dim3(grid), dim3(kCtaThreads), params, smem_bytes, st);
 }
 
-cudaError_t fused_ctas_per_sm(int occupancy, size_t smem_bytes, int* per_sm) {
-  FusedKernel k = pick(occupancy, false);
-  cudaError_t e = allow_smem(k, occupancy, false, smem_bytes);
+cudaError_t fused_ctas_per_sm(int occupancy, size_t smem_bytes, int* per_sm, int kind, int unroll) {
+  FusedKernel k = pick(occupancy, false, kind, unroll);
+  cudaError_t e = allow_smem(k, smem_bytes);
   if (e != cudaSuccess) return e;
   return cudaOccupancyMaxActiveBlocksPerMultiprocessor(per_sm, reinterpret_cast<const void*>(k), kCtaThreads,
                                                        smem_bytes);

@@ -52,7 +52,7 @@ constexpr int kNoAllocOccupancy = 4;
 
 // descriptor table first, then a workspace laid out by ws_layout(kMaxFeat)
 constexpr size_t kDescBytes = sizeof(FeatStatic) * (size_t)kMaxFeat;
-constexpr size_t kWsBytesMax = ws_layout(kMaxFeat).total;
+constexpr size_t kWsBytesMax = ws_layout(kMaxFeat).long_list;  // long-bag splitting stays off here
 constexpr size_t kNoAllocScratchBytes = kDescBytes + ((kWsBytesMax + 255) / 256) * 256;
 
 // The name below is a host-side stand-in for the device array: host code must
@@ -122,7 +122,7 @@ int eb_forward_packed_noalloc(int device, int num_features, const int64_t* rows,
   if (batch < 0) return fail(EB_ERR_INVALID_ARG, "negative batch");
   if (index_dtype != EB_I32 && index_dtype != EB_I64) return fail(EB_ERR_INVALID_ARG, "bad index_dtype %d", index_dtype);
   if (device < 0 || device >= kMaxDevices) return fail(EB_ERR_INVALID_ARG, "device %d out of range", device);
-  if (ws_layout(num_features).total + kDescBytes > kNoAllocScratchBytes)
+  if (ws_layout(num_features).long_list + kDescBytes > kNoAllocScratchBytes)
     return fail(EB_ERR_TOO_LARGE, "scratch array too small for %d features", num_features);
   if ((long double)batch * (long double)num_features >= 2147483648.0L)
     return fail(EB_ERR_TOO_LARGE, "batch * num_features must stay below 2^31 tiles");

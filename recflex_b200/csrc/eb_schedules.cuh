@@ -43,6 +43,9 @@ struct TileCtx {
   int32_t out_dt;    // element type of the output: 0 = fp32, 1 = bfloat16, 2 = binary16
   int32_t es_shift;  // log2 of the output element size: 2 or 1
   uint32_t* status;
+  LongBagList* long_list;  // where bags too long for one warp are handed over (used when long_bytes > 0)
+  int64_t long_bytes;      // a bag gathering at least this many bytes is handed over; 0 = never
+  int32_t feat;            // the feature's number (for the hand-over)
   int32_t dim;
   int32_t row_bytes;
   int32_t lg_group;
@@ -188,9 +191,14 @@ __device__ __forceinline__ void store_vals(char* dstb, const float (&a)[V], int 
   } else {
     if constexpr (V == 8) {
       if (vec_ok == 2) {
+#ifdef EB_ROWS_INLINE
+        asm volatile("st.global.cs.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "f"(a[0]), "f"(a[1]),
+                     "f"(a[2]), "f"(a[3]), "f"(a[4]), "f"(a[5]), "f"(a[6]), "f"(a[7]));
+#else
         asm volatile("st.global.cs.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "f"(a[0]), "f"(a[1]),
                      "f"(a[2]), "f"(a[3]), "f"(a[4]), "f"(a[5]), "f"(a[6]), "f"(a[7])
                      : "memory");
+#endif
         return;
       }
     }
@@ -291,29 +299,39 @@ static __device__ __noinline__ Chunk repair_chunk(const TileCtx& c, int64_t a_ra
 // One warp vote decides whether the 33 boundaries are already a non-decreasing sequence inside [0, nnz] spanning at
 // most 2^30 entries (the normal case: a handful of instructions, 32-bit when the batch's integers are); only
 // otherwise is the sequence repaired.  Must be called by all 32 lanes.
+// 32-bit boundaries: this lane's boundary `a` and the boundary `end` after the chunk's last bag -> Chunk.
+__device__ __forceinline__ Chunk chunk_from32(const TileCtx& c, int a, int end, int lane) {
+  const int nnz = c.nnz > 0x7fffffff ? 0x7fffffff : (int)c.nnz;
+  int nxt = __shfl_down_sync(kFull, a, 1);
+  if (lane == 31) nxt = end;
+  const int a0 = __shfl_sync(kFull, a, 0);
+  const bool good = a >= 0 && a <= nxt && nxt <= nnz && (unsigned)(end - a0) <= 0x3fffffffu;
+  if (__all_sync(kFull, good)) {
+    Chunk ch;
+    ch.e0 = a0;
+    ch.lo = a - a0;
+    ch.hi = nxt - a0;
+    ch.n = end - a0;
+    return ch;
+  }
+  return repair_chunk(c, (int64_t)a, (int64_t)end, lane);
+}
+
+// Boundary number `pos` of a feature with 32-bit offsets (an offsets array without end entry lacks the last one).
+__device__ __forceinline__ int boundary32(const TileCtx& c, int64_t pos) {
+  if (!c.has_end && pos >= c.batch) return c.nnz > 0x7fffffff ? 0x7fffffff : (int)c.nnz;
+  return __ldg(reinterpret_cast<const int*>(c.offsets) + pos);
+}
+
 template <bool IDX64>
 __device__ __forceinline__ Chunk load_chunk(const TileCtx& c, int64_t bb, int nb, int lane) {
   const int li = lane <= nb ? lane : nb;
   Chunk ch;
   if constexpr (!IDX64) {
-    const int nnz = c.nnz > 0x7fffffff ? 0x7fffffff : (int)c.nnz;
-    const int* op = reinterpret_cast<const int*>(c.offsets);
-    const bool past = !c.has_end && bb + li >= c.batch;  // the one boundary an offsets array without end entry lacks
-    const int a = past ? nnz : __ldg(op + bb + li);
+    const int a = boundary32(c, bb + li);
     int end = __shfl_sync(kFull, a, 31);
-    if (nb == 32) end = (!c.has_end && bb + 32 >= c.batch) ? nnz : __ldg(op + bb + 32);
-    int nxt = __shfl_down_sync(kFull, a, 1);
-    if (lane == 31) nxt = end;
-    const int a0 = __shfl_sync(kFull, a, 0);
-    const bool good = a >= 0 && a <= nxt && nxt <= nnz && (unsigned)(end - a0) <= 0x3fffffffu;
-    if (__all_sync(kFull, good)) {
-      ch.e0 = a0;
-      ch.lo = a - a0;
-      ch.hi = nxt - a0;
-      ch.n = end - a0;
-      return ch;
-    }
-    return repair_chunk(c, (int64_t)a, (int64_t)end, lane);
+    if (nb == 32) end = boundary32(c, bb + 32);
+    return chunk_from32(c, a, end, lane);
   } else {
     const int64_t a = raw_offset(c, bb + li);
     int64_t end = __shfl_sync(kFull, a, 31);
@@ -719,15 +737,33 @@ __device__ __forceinline__ bool issue_rows(const TileCtx& c, const char* tcol, b
 constexpr int kBagItems = 34;        // per-warp list of a chunk's non-empty bags: 32 + sentinel, padded
 constexpr int kNoEnd = 0x7fffffff;   // "this bag does not end inside my piece"
 
-// Next list item; an end beyond the piece never matches a position.
-__device__ __forceinline__ void next_bag(unsigned& item_addr, int e_end, int& kb, int& kend) {
-  item_addr += 8;
-  int end;
-  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(end), "=r"(kb) : "r"(item_addr));
-  kend = end > e_end ? kNoEnd : end;
+
+// A slot's cursor in the chunk's list of non-empty bags.  The item after the current bag is fetched one bag ahead, so
+// that the shared-memory latency is not in the chain bag end -> next end -> next comparison.
+struct BagCursor {
+  const int2* p;  // the prefetched item (shared memory)
+  int2 nxt;       // the item after the current bag
+  __device__ __forceinline__ void init(const int2* current_item) {
+    p = current_item + 1;
+    nxt = *p;
+  }
+  // Make the next list item the current bag; an end beyond the piece never matches a position.
+  __device__ __forceinline__ void advance(int e_end, int& kb, int& kend) {
+    kb = nxt.y;
+    kend = nxt.x > e_end ? kNoEnd : nxt.x;
+    nxt = *++p;
+  }
+};
+
+// Stores of the stream walk.  FS (fast store) = fp32 output whose alignment allows the widest store: no run-time
+// choice is left in the walk's hot block.
+template <int V, bool FS>
+__device__ __forceinline__ void walk_store(char* dst, const float (&a)[V], int ov, int dt) {
+  if constexpr (FS) store_vals<V>(dst, a, V == 8 ? 2 : 1, 0);
+  else store_vals<V>(dst, a, ov, dt);
 }
 
-template <typename T, int V, int U, bool IDX64, int D = 0>
+template <typename T, int V, int U, bool IDX64, int D = 0, bool FS = false>
 __device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_t b1, int lane, int2* items,
                                             unsigned char* ring = nullptr) {
   static_assert(D == 0 || V * sizeof(T) == 16, "the ring holds 16-byte lane cells");
@@ -735,19 +771,89 @@ __device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_
   using IdxT = typename IdxOf<IDX64>::type;
   const int lgG = c.lg_group, lgR = 5 - lgG, G = 1 << lgG, R = 1 << lgR;
   const int r = lane >> lgG, cl = lane & (G - 1);
-  const unsigned ld_bytes = (unsigned)c.out_ld << c.es_shift;  // the entry points refuse rows of 4 GB and more
-  const int dt = c.out_dt;
+  const unsigned ld_bytes = FS ? (unsigned)c.out_ld * 4u : (unsigned)c.out_ld << c.es_shift;  // rows stay below 4 GB
+  const int dt = FS ? 0 : c.out_dt;
   const unsigned rows32 = c.rows > 0x80000000ll ? 0x80000000u : (unsigned)c.rows;
-  const int ov = c.out_vec;
+  const int ov = FS ? (V == 8 ? 2 : 1) : c.out_vec;
   for (int xc = 0; xc < c.nx; ++xc) {
     const int cs = (xc * G + cl) * V;
     const bool col_ok = cs < c.dim;
     const char* tcol = c.table + (size_t)cs * sizeof(T);
-    for (int64_t bb = b0; bb < b1; bb += 32) {
-      const int nb = (int)((b1 - bb) < 32 ? (b1 - bb) : 32);
-      const Chunk ch = load_chunk<IDX64>(c, bb, nb, lane);
+    // 32-bit offsets: the boundaries of the next two chunks are fetched while this one is walked, so that a chunk
+    // starts without waiting for its offsets (lane i holds boundary pos0 + min(i, bags left))
+    auto bounds_at = [&](int64_t pos0) -> int {
+      if (pos0 > b1) return 0;
+      const int64_t cnt = (b1 - pos0) < 32 ? (b1 - pos0) : 32;
+      return boundary32(c, pos0 + (lane < cnt ? lane : cnt));
+    };
+    int a_cur = 0, a_nxt = 0;
+    if constexpr (!IDX64) {
+      a_cur = bounds_at(b0);
+      a_nxt = bounds_at(b0 + 32);
+    }
+    // a bag of this many entries or more is handed to eb_longbag_kernel (never, when the feature is off)
+    // (rows wider than one column pass are always pooled in place: every pass would have to take the same decision)
+    const int long_len = (IDX64 || c.long_bytes <= 0 || c.nx > 1) ? kNoEnd
+                         : (int)((c.long_bytes + c.row_bytes - 1) / c.row_bytes > 0x3fffffff
+                                     ? 0x3fffffff : (c.long_bytes + c.row_bytes - 1) / c.row_bytes);
+    int nb = 0;
+    for (int64_t bb = b0; bb < b1; bb += nb) {
+      // chunks start at multiples of 32 bags from b0, except right after a handed-over bag
+      nb = 32 - (int)((bb - b0) & 31);
+      if (b1 - bb < nb) nb = (int)(b1 - bb);
+      Chunk ch;
+      if constexpr (!IDX64) {
+        const int a_fut = bounds_at(bb + 64);
+        ch = chunk_from32(c, a_cur, nb == 32 ? __shfl_sync(kFull, a_nxt, 0) : __shfl_sync(kFull, a_cur, 31), lane);
+#ifdef EB_NO_LONGBAG
+        const unsigned too_long = 0u;
+#else
+        const unsigned too_long = __ballot_sync(kFull, ch.hi - ch.lo >= long_len);
+#endif
+        if (too_long == 0u) {
+          a_cur = a_nxt;
+          a_nxt = a_fut;
+        } else {
+          // rare: walk only the bags before the first long one now (or hand that bag over, when it comes first) and
+          // re-read the boundaries for the shortened schedule of chunks
+          const int p = __ffs(too_long) - 1;
+          bool handed = false;
+          if (p == 0) {
+            unsigned slot = 0;
+            if (lane == 0) slot = atomicAdd(&c.long_list->count, 1u);
+            slot = __shfl_sync(kFull, slot, 0);
+            handed = slot < (unsigned)kMaxLongBags;  // a full list takes no more: the bag is walked in place
+            if (handed && lane == 0) {
+              LongBag lb;
+              lb.feat = c.feat;
+              lb.pad_ = 0;
+              lb.bag = bb;
+              lb.begin = ch.e0 + ch.lo;
+              lb.end = ch.e0 + ch.hi;
+              c.long_list->item[slot] = lb;
+            }
+          }
+          if (p == 0 && handed) {
+            nb = 1;  // skipped here: eb_longbag_kernel pools it
+            a_cur = boundary32(c, bb + 1 + min(lane, min(31 - (int)((bb + 1 - b0) & 31), (int)(b1 - bb - 1))));
+            a_nxt = bounds_at(bb + 1 + (32 - ((bb + 1 - b0) & 31)));
+            continue;
+          }
+          const int keep = p == 0 ? 1 : p;  // a full list: the long bag is walked in place, alone
+          const int a_end = __shfl_sync(kFull, a_cur, keep);
+          ch = chunk_from32(c, lane <= keep ? a_cur : a_end, a_end, lane);
+          nb = keep;
+          const int64_t nbb = bb + nb;
+          int nnb = 32 - (int)((nbb - b0) & 31);
+          if (b1 - nbb < nnb) nnb = (int)(b1 - nbb);
+          a_cur = nbb < b1 ? boundary32(c, nbb + min(lane, nnb)) : 0;
+          a_nxt = bounds_at(nbb + nnb);
+        }
+      } else {
+        ch = load_chunk<IDX64>(c, bb, nb, lane);
+      }
       const int n = ch.n;
-      char* const orow = chunk_out(c, bb) + ((size_t)cs << c.es_shift);
+      char* const orow = chunk_out(c, bb) + ((size_t)cs << (FS ? 2 : c.es_shift));
       const bool nonempty = ch.hi > ch.lo;
       const unsigned nz = __ballot_sync(kFull, nonempty);
 
@@ -759,7 +865,7 @@ __device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_
         zero_vals<V>(z);
         while (em) {
           const int i = (int)__fns(em, 0, r + 1);
-          if (i >= 0 && col_ok) store_vals<V>(orow + (size_t)i * ld_bytes, z, ov, dt);
+          if (i >= 0 && col_ok) walk_store<V, FS>(orow + (size_t)i * ld_bytes, z, ov, dt);
           for (int k = 0; k < R && em; ++k) em &= em - 1;
         }
       }
@@ -785,7 +891,8 @@ __device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_
       }
       int kend = __shfl_sync(kFull, ch.hi, kb);
       const int klo = __shfl_sync(kFull, ch.lo, kb);
-      unsigned item_addr = smem_addr(items) + 8u * (unsigned)__popc(nz & ((1u << kb) - 1u));  // its place in the list
+      BagCursor cur;
+      cur.init(items + __popc(nz & ((1u << kb) - 1u)));  // its place in the list
       const bool began_earlier = klo < s && e_end > s;
       const bool had_head = began_earlier && kend <= e_end;  // it ends inside my piece: its first part lies in earlier pieces
       const bool inside_one = began_earlier && kend > e_end;  // my whole piece lies inside one bag
@@ -817,9 +924,9 @@ __device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_
             for (int u = 0; u < U; ++u) {
               Ops::add(acc, rows[u]);
               if (++e == kend) {
-                if (col_ok) store_vals<V>(orow + (size_t)((unsigned)kb * (uint64_t)ld_bytes), acc, ov, dt);
+                if (col_ok) walk_store<V, FS>(orow + (size_t)((unsigned)kb * (uint64_t)ld_bytes), acc, ov, dt);
                 zero_vals<V>(acc);
-                next_bag(item_addr, e_end, kb, kend);
+                cur.advance(e_end, kb, kend);
               }
             }
           }
@@ -829,84 +936,95 @@ __device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_
         const int nsteps = (ls + U - 1) / U;
         IdxT idx[U];
         bool bad = false;
-        // indices of macro-step 0; `plain`: every slot has U real entries there and every index is a row of the table
-        bool plain = false;
-        if (U <= q) {
-          bool valid = true;
+        // indices of macro-step 0; `full`: every slot has U real entries there, so they were fetched without guards
+        bool full = U <= q;
+        if (full) {
 #pragma unroll
-          for (int u = 0; u < U; ++u) {
-            idx[u] = __ldg(vp + s + u);
-            if constexpr (IDX64) valid = valid && (uint64_t)idx[u] < (uint64_t)c.rows;
-            else valid = valid && (unsigned)idx[u] < rows32;
-          }
-          plain = __all_sync(kFull, valid);
+          for (int u = 0; u < U; ++u) idx[u] = __ldg(vp + s + u);
         } else {
           load_indices<U, IDX64>(vp, s, e_end, col_ok, idx);
         }
-        unsigned cell_in = cell, cell_out = cell;  // ring cursors
+        unsigned cell_in = cell;  // ring cursors: copies go in by shared-memory address, rows come out by pointer
         const unsigned cell_end = cell + D * U * 512;
+        const unsigned char* const ring_lane = ring + lane * 16;
+        int out_off = 0;
         // iteration m issues the copies of macro-step m + D - 1, fetches the indices of macro-step m + D and, from
-        // m = 0 on, consumes macro-step m
+        // m = 0 on, consumes macro-step m.  The indices fetched in one iteration are first looked at in the next
+        // one (validity test and copies), a whole macro-step of work later.
 #pragma unroll 1
         for (int m = 1 - D; m < nsteps; ++m) {
           const int first = s + (m + D - 1) * U;
           if (m + D - 1 >= nsteps) {
             // past every piece's end: an empty copy group keeps the group count in step
-          } else if (plain) {
-            if (col_ok) {
+          } else {
+            bool plain = false;
+            if (full) {
+              bool valid = true;
 #pragma unroll
               for (int u = 0; u < U; ++u) {
-                if constexpr (IDX64) cp_async16(cell_in + u * 512, tcol + idx[u] * (int64_t)c.row_bytes, 16u);
-                else cp_async16(cell_in + u * 512, tcol + (uint64_t)(unsigned)idx[u] * (unsigned)c.row_bytes, 16u);
+                if constexpr (IDX64) valid = valid && (uint64_t)idx[u] < (uint64_t)c.rows;
+                else valid = valid && (unsigned)idx[u] < rows32;
               }
+              plain = __all_sync(kFull, valid);
             }
-          } else {
-            bad |= issue_rows<T, U, IDX64>(c, tcol, col_ok, idx, first, e_end, cell_in);
+            if (plain) {
+              // every slot has U real entries with valid indices: no predicate on the copies
+              if (col_ok) {
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                  if constexpr (IDX64) cp_async16(cell_in + u * 512, tcol + idx[u] * (int64_t)c.row_bytes, 16u);
+                  else cp_async16(cell_in + u * 512, tcol + (uint64_t)(unsigned)idx[u] * (unsigned)c.row_bytes, 16u);
+                }
+              }
+            } else {
+              bad |= issue_rows<T, U, IDX64>(c, tcol, col_ok, idx, first, e_end, cell_in);
+            }
           }
           cp_async_commit();
-          if ((m + D + 1) * U <= q) {
-            bool valid = true;
+          full = (m + D + 1) * U <= q;
+          if (full) {
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-              idx[u] = __ldg(vp + first + U + u);
-              if constexpr (IDX64) valid = valid && (uint64_t)idx[u] < (uint64_t)c.rows;
-              else valid = valid && (unsigned)idx[u] < rows32;
-            }
-            plain = __all_sync(kFull, valid);
-          } else {
-            if (m + D < nsteps) load_indices<U, IDX64>(vp, first + U, e_end, col_ok, idx);
-            plain = false;
+            for (int u = 0; u < U; ++u) idx[u] = __ldg(vp + first + U + u);
+          } else if (m + D < nsteps) {
+            load_indices<U, IDX64>(vp, first + U, e_end, col_ok, idx);
           }
           cell_in += U * 512;
           if (cell_in == cell_end) cell_in = cell;
           if (m < 0) continue;
           cp_async_wait<D - 1>();
+#ifndef EB_ROWS_INLINE
           typename Ops::Raw rows[U];
 #pragma unroll
-          for (int u = 0; u < U; ++u) rows[u] = lds16(cell_out + u * 512);
+          for (int u = 0; u < U; ++u) rows[u] = *reinterpret_cast<const uint4*>(ring_lane + out_off + u * 512);
+#define EB_ROW(u) rows[u]
+#else
+#define EB_ROW(u) (*reinterpret_cast<const uint4*>(ring_lane + out_off + (u) * 512))
+#endif
           if (__all_sync(kFull, e + U < kend)) {
 #pragma unroll
-            for (int u = 0; u < U; ++u) Ops::add(acc, rows[u]);
+            for (int u = 0; u < U; ++u) Ops::add(acc, EB_ROW(u));
             e += U;
           } else {
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-              Ops::add(acc, rows[u]);
+              Ops::add(acc, EB_ROW(u));
               if (++e == kend) {
-                if (col_ok) store_vals<V>(orow + (size_t)((unsigned)kb * (uint64_t)ld_bytes), acc, ov, dt);
+                if (col_ok) walk_store<V, FS>(orow + (size_t)((unsigned)kb * (uint64_t)ld_bytes), acc, ov, dt);
                 zero_vals<V>(acc);
-                next_bag(item_addr, e_end, kb, kend);
+                cur.advance(e_end, kb, kend);
               }
             }
           }
-          cell_out += U * 512;
-          if (cell_out == cell_end) cell_out = cell;
+          out_off += U * 512;
+          if (out_off == D * U * 512) out_off = 0;
         }
+#undef EB_ROW
         cp_async_wait<0>();  // the ring is reused by the next chunk
         if (bad) flag(c.status, kStatusBadIndex);
       }
 
       // patch the bags cut by piece boundaries
+      asm volatile("" ::: "memory");  // the head partials are read back below: keep those loads after the walk's stores
       if (R > 1 && __any_sync(kFull, had_head)) {
         bool f = !inside_one;  // my tail starts a new run unless my whole piece lies inside one bag
 #pragma unroll
@@ -929,7 +1047,7 @@ __device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_
           char* dst = orow + (size_t)((unsigned)head_bag * (uint64_t)ld_bytes);
           float hv[V];
           reload_add<V>(dst, prev, hv, ov, dt);
-          store_vals<V>(dst, hv, ov, dt);
+          walk_store<V, FS>(dst, hv, ov, dt);
         }
       }
     }

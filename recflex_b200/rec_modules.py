@@ -158,6 +158,11 @@ class FeatEmbed(nn.Module):
         _lib.check(self._lib.eb_set_output_dtype(self._h, self._OUT_DTYPES[dtype]))
         self.output_dtype = dtype
 
+    def set_long_bag_split(self, min_bytes: int) -> None:
+        """Bags whose rows add up to `min_bytes` or more (default 1 MB) are pooled by many warps in a second kernel
+        instead of by the one warp that meets them; 0 pools every bag in place."""
+        _lib.check(self._lib.eb_set_long_bag_split(self._h, int(min_bytes)))
+
     def _check_out(self, out: Optional[torch.Tensor], batch: int) -> torch.Tensor:
         if out is None:
             return torch.empty((batch, self.output_units), dtype=self.output_dtype, device=self.device)
@@ -376,6 +381,12 @@ class FeatEmbed(nn.Module):
         n = C.c_int()
         _lib.check(self._lib.eb_kernel_times(self._h, buf, 256, C.byref(n)))
         return [float(buf[i]) for i in range(n.value)]
+
+    def last_binding(self) -> List[int]:
+        """Bags per warp tile the device chose for every feature in the last forward (synchronises)."""
+        arr = (C.c_int32 * self.num_features)()
+        _lib.check(self._lib.eb_last_binding(self._h, C.c_void_p(self._ws_ptr), self._stream(), arr))
+        return [int(x) for x in arr]
 
     def check_status(self) -> None:
         """Raise if the last forward met an out-of-range index or non-monotone offsets (synchronises)."""

@@ -143,9 +143,16 @@ class Tuner:
     loads `sample_batch_nums` batches from the data files)."""
 
     def __init__(self, module: FeatEmbed, batches: Sequence[Tuple[Sequence[torch.Tensor], Sequence[torch.Tensor]]],
-                 config: Optional[TuneConfig] = None):
+                 config: Optional[TuneConfig] = None, candidates_from: Optional[Sequence[Sequence[Optional[str]]]] = None):
+        """`candidates_from`: per feature, the schedule kinds it may use (what `parser.parse_schedule_types` returns
+        for a `schedule_config.txt`; unknown names arrive as None and are ignored).  The reference restricts every
+        feature's candidates to the classes its schedule_config line names (tuner.py:70-81)."""
         if not batches:
             raise ValueError("at least one sampled batch is needed")
+        if candidates_from is not None and len(candidates_from) != module.num_features:
+            raise ValueError(f"candidates_from has {len(candidates_from)} entries for {module.num_features} features")
+        self.candidates_from = None if candidates_from is None else [
+            tuple(dict.fromkeys(k for k in kinds if k is not None)) for kinds in candidates_from]
         self.module = module
         self.batches = list(batches)
         self.config = config or TuneConfig()
@@ -163,7 +170,12 @@ class Tuner:
         """Candidate schedules of one feature (reference: `gen_feat_sched_param_candidates`, tuner.py:76-81)."""
         st = self.stats[feat]
         cands = []
-        for kind in self.config.kinds:
+        kinds = self.config.kinds
+        if self.candidates_from is not None:
+            kinds = self.candidates_from[feat]
+            if not kinds:
+                raise ValueError(f"feature {feat}: the schedule configuration names no schedule this library knows")
+        for kind in kinds:
             for u in self.config.unrolls:
                 if kind == "group" and st.mean_len > 64:
                     continue  # a slot walking hundreds of rows alone leaves the other slots idle
@@ -183,7 +195,7 @@ class Tuner:
             key = (f,)
             if self.config.cluster:
                 key = (int(t.shape[1]), str(t.dtype), int(round(math.log2(max(int(t.shape[0]), 1)) / 2)),
-                       self.stats[f].bucket())
+                       self.stats[f].bucket(), self.candidates_from[f] if self.candidates_from is not None else None)
             groups.setdefault(key, []).append(f)
         return groups
 
@@ -386,11 +398,39 @@ class Tuner:
         ms = self.fused_ms(scheds, occupancy)
         return TuneResult(scheds, occupancy, {}, {occupancy: ms}, self.stats)
 
+    def tune_fixed_thread_binding(self, result: TuneResult, choice: str = "max") -> Tuple[List[int], float, float]:
+        """Ablation (reference: `tune_fixed_thread_binding`, tuner.py:312-357): replace the per-batch binding by a
+        fixed one.  The tile counts the device chose for every sampled batch under `result`'s schedules are reduced
+        per feature to their maximum or mean (`choice`), turned back into a fixed bags-per-tile, installed, and the
+        kernel is timed.  Returns (fixed bags per tile, kernel ms with the fixed binding, kernel ms with the
+        run-time binding); `result`'s schedules are back in place afterwards."""
+        if choice not in ("max", "mean"):
+            raise ValueError("choice must be 'max' or 'mean'")
+        mod = self.module
+        result.apply(mod)
+        tiles = []
+        for values, offsets in self.batches:
+            mod(values, offsets)
+            batch = offsets[0].numel() - 1
+            tiles.append([-(-batch // n) for n in mod.last_binding()])
+        fixed = []
+        for f in range(self.num_feats):
+            per_batch = [t[f] for t in tiles]
+            want = max(per_batch) if choice == "max" else max(1, sum(per_batch) // len(per_batch))
+            batch = self.batches[0][1][f].numel() - 1
+            n = max(1, min(1024, batch // max(want, 1)))
+            fixed.append(1 << (n.bit_length() - 1))  # bags per tile are powers of two
+        dynamic_ms = self.fused_ms(result.schedules, result.occupancy)
+        pinned = [Schedule(s.kind, s.unroll, fixed[f]) for f, s in enumerate(result.schedules)]
+        fixed_ms = self.fused_ms(pinned, result.occupancy)
+        result.apply(mod)
+        return fixed, fixed_ms, dynamic_ms
+
     def retune(self, result: TuneResult, new_batches) -> TuneResult:
         """Re-run the local stage only for features whose statistics moved bucket on `new_batches`, keep the
         occupancy sweep (distribution shift)."""
         self.module.set_kernel_overlap(0)
-        fresh = Tuner(self.module, new_batches, self.config)
+        fresh = Tuner(self.module, new_batches, self.config, self.candidates_from)
         moved = set(needs_retune(result.stats, fresh.stats)) if result.stats else set(range(self.num_feats))
         if not moved:
             fresh.module.set_schedules(result.schedules, occupancy=result.occupancy)
@@ -443,6 +483,11 @@ def main(argv=None) -> None:
     p.add_argument("--naive", action="store_true", help="ablation: time candidates alone (no interference)")
     p.add_argument("--mutation-feat-id", type=int, default=-1)
     p.add_argument("--no-cluster", action="store_true")
+    p.add_argument("--schedule-config", type=str, default="",
+                   help="a schedule_config.txt of the reference: restricts every feature's candidates to the classes "
+                        "its line names (mapped to this library's kinds by parser.SCHEDULE_KINDS)")
+    p.add_argument("--fixed-thread-binding", choices=["", "max", "mean"], default="",
+                   help="ablation: also time the tuned kernel with a fixed bags-per-tile per feature")
     p.add_argument("--out", type=str, required=True)
     args = p.parse_args(argv)
 
@@ -455,7 +500,12 @@ def main(argv=None) -> None:
         v, o = synth.gen_batch(cfg, seed=7000 + i)
         batches.append(([torch.from_numpy(x).to(dev) for x in v], [torch.from_numpy(x).to(dev) for x in o]))
     tc = TuneConfig(occupancies=tuple(int(x) for x in args.occupancies.split(",")), cluster=not args.no_cluster)
-    tuner = Tuner(mod, batches, tc)
+    allowed = None
+    if args.schedule_config:
+        from .parser import parse_schedule_types
+
+        allowed = parse_schedule_types(args.schedule_config)
+    tuner = Tuner(mod, batches, tc, candidates_from=allowed)
     t0 = time.time()
     base_ms = tuner.fused_ms([Schedule("auto") for _ in range(mod.num_features)], 4)
     res = tuner.tune_naive() if args.naive else tuner.tune()
@@ -465,6 +515,10 @@ def main(argv=None) -> None:
     if args.mutation_feat_id >= 0:
         times, pick = tuner.mutation_validation(res, args.mutation_feat_id)
         extra["mutation"] = {"feature": args.mutation_feat_id, "times_ms": times, "pick": pick}
+    if args.fixed_thread_binding:
+        fixed, fixed_ms, dyn_ms = tuner.tune_fixed_thread_binding(res, args.fixed_thread_binding)
+        extra["fixed_thread_binding"] = {"choice": args.fixed_thread_binding, "bags_per_tile": fixed,
+                                         "fixed_ms": fixed_ms, "runtime_binding_ms": dyn_ms}
     res.save(args.out, **extra)
     print(json.dumps({k: v for k, v in extra.items() if k != "mutation"}))
     print("occupancy", res.occupancy, "global_ms", res.global_ms)

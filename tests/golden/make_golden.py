@@ -31,7 +31,9 @@ import torch.nn.functional as F
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("RECFLEX_REF", "/root/reference")
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("RECFLEX_REF")
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("usage: make_golden.py <path to the RecFlex checkout>  (or set RECFLEX_REF)")
 sys.dont_write_bytecode = True
 sys.path.insert(0, REF)
 sys.path.insert(0, os.path.join(REF, "examples"))

@@ -70,3 +70,36 @@ def test_naive_tuning_and_retune():
     sv = [np.concatenate([values[0]] * 8)] + list(values[1:6])
     so = [offsets[0] * 8] + list(offsets[1:6])
     check_against_oracle(out, tables[:6], sv, so, "f32")
+
+
+def test_schedule_config_restricts_candidates_and_fixed_thread_binding(tmp_path):
+    """A reference schedule_config.txt names each feature's candidate classes (RecFlex/parser.py:19-26); the tuner
+    must pick only among them.  Then the fixed-thread-binding ablation (RecFlex/tuning/tuner.py:312-357)."""
+    from recflex_b200 import _lib
+    from recflex_b200.parser import parse_schedule_types
+
+    cfg, tables, values, offsets = small_model(2, 0.02, 1024)
+    tables, values, offsets = tables[:8], values[:8], offsets[:8]
+    lines = ["OneHotSchedule,WarpPerSampleSchedule", "ReduceByKeySchedule", "MultiBlockPerSampleSchedule,NoSuchSchedule",
+             "OneBlockMultiSampleSchedule", "WarpPerSampleSchedule", "ReduceByKeySchedule,MultiBlockPerSampleSchedule",
+             "OneHotMultiBlockSchedule", "MultiBlockPerSampleSchedule"]
+    path = os.path.join(tmp_path, "schedule_config.txt")
+    with open(path, "w") as f:
+        f.write("\n".join(lines) + "\n")
+    allowed = parse_schedule_types(path)
+    mod = FeatEmbed("cuda:0", embed_tables=device_tables(tables))
+    dv, do = to_device(values), to_device(offsets)
+    tc = TuneConfig(occupancies=(4,), reps=1, global_reps=1, uniform_portfolio=(), hybrid_min_len=(), refine_top=0)
+    tuner = Tuner(mod, [(dv, do)], tc, candidates_from=allowed)
+    res = tuner.tune()
+    for f, s in enumerate(res.schedules):
+        names = {k for k in allowed[f] if k is not None}
+        assert _lib.SCHED_NAMES[s.kind] in names, (f, s, names)
+    check_against_oracle(mod(dv, do), tables, values, offsets, "f32")
+    fixed, fixed_ms, dyn_ms = tuner.tune_fixed_thread_binding(res, "max")
+    assert len(fixed) == 8 and all(n >= 1 and n & (n - 1) == 0 for n in fixed) and fixed_ms > 0 and dyn_ms > 0
+    got, _ = mod.get_schedules()
+    assert all(s.bags_per_tile == 0 for s in got)  # the run-time binding is back
+    pinned = [Schedule(s.kind, s.unroll, fixed[f]) for f, s in enumerate(res.schedules)]
+    mod.set_schedules(pinned, occupancy=res.occupancy)
+    check_against_oracle(mod(dv, do), tables, values, offsets, "f32")
