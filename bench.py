@@ -527,6 +527,41 @@ def run_ours(args):
         t_e2e_bf16 = float(t[2]) if t_e2e_bf16 is not None else None
         t_strong = float(t[3]) if t_strong is not None else None
 
+    # ---- the reference's end-to-end model (embedding -> MLP [1024, 256, 128] -> sigmoid; RecFlex/rec_modules.py:143-179,
+    # examples/end_to_end.py:39-51) on the same batches, MLP in fp32 and in bf16 (the embedding then writes bf16 rows) ----
+    recom = None
+    if world == 1 and not args.no_e2e:
+        from recflex_b200.rec_modules import RecomModel
+
+        recom = {}
+        per_feature = ([torch.from_numpy(v).to(dev) for v in first[0]], [torch.from_numpy(o).to(dev) for o in first[1]])
+        for name, dt in (("fp32", torch.float32), ("bf16", torch.bfloat16)):
+            try:
+                torch.manual_seed(0)
+                model = RecomModel([1024, 256, 128], dev, embed_tables=tables, mlp_dtype=dt)
+                scheds, occ_m = mod.get_schedules()
+                model.embed_layer.set_schedules(scheds, occupancy=occ_m)
+                if overlap:
+                    model.embed_layer.set_kernel_overlap(overlap)
+                with torch.no_grad():
+                    for _ in range(3):
+                        y = model(*per_feature)
+                    torch.cuda.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    for _ in range(max(5, K // 2)):
+                        y = model(*per_feature)
+                    e1.record()
+                    e1.synchronize()
+                recom[name + "_ms_per_batch"] = e0.elapsed_time(e1) / max(5, K // 2)
+                recom[name + "_output_mean"] = float(y.float().mean())
+                del model, y
+            except Exception as exc:
+                recom[name + "_unavailable"] = f"{type(exc).__name__}: {exc}"[:200]
+        recom["note"] = "RecomModel forward on one resident batch: fused embedding + torch MLP; bf16 = bfloat16 MLP fed by bfloat16 embedding rows"
+        del per_feature
+        torch.cuda.empty_cache()
+
     # ---- N > 1: the table-wise sharded configuration on the same GPUs (frees this workload's tables first) ----
     sharded = None
     if world > 1 and not args.no_sharded and args.workload == "cfg3" and args.row_scale == 1.0 and not args.batch:
@@ -593,6 +628,8 @@ def run_ours(args):
                               "efficiency": (t_dev / K) / (world * t_strong / K),
                               "note": "one batch split over the GPUs; efficiency = time of one GPU pooling the whole "
                                       "batch / (N x time of the split step)"}
+        if recom:
+            line["recom_model"] = recom
         if sharded is not None:
             line["sharded"] = sharded
         if world == 1 and args.workload in ("cfg1", "cfg2", "cfg5") and args.row_scale == 1.0:

@@ -330,6 +330,8 @@ int eb_set_output_dtype(eb_handle* h, int out_dtype);
  * than the pooling runs.  The caller orders consumers after all ranks' copy
  * streams, and must not reuse `send` before `copy_stream` is done with it.
  * batch must be a multiple of world * chunks; world <= 16, chunks <= 64.
+ * The flags live in `workspace` and count calls: zero-fill a workspace once
+ * before its first use here.
  * Returns EB_ERR_UNSUPPORTED when the driver has no stream memory operations.
  */
 int eb_forward_exchange(eb_handle* h, int64_t batch, const void* const* values_ptrs,

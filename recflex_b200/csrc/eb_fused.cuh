@@ -31,10 +31,10 @@ namespace ebk {
 // EB_SCHED_STREAM: the register walk.  FS: fp32 output aligned for the widest store (see walk_store).
 #define EB_DISPATCH_STREAM_T(T, V, I64, FS)                                           \
   switch (fs.unroll) {                                                                \
-    case 1: tile_stream<T, V, 1, I64, 0, FS>(ctx, b0, b1, lane, items); break;        \
-    case 2: tile_stream<T, V, 2, I64, 0, FS>(ctx, b0, b1, lane, items); break;        \
-    case 4: tile_stream<T, V, 4, I64, 0, FS>(ctx, b0, b1, lane, items); break;        \
-    default: tile_stream<T, V, 8, I64, 0, FS>(ctx, b0, b1, lane, items); break;       \
+    case 1: tile_stream<T, V, 1, I64, 0, FS>(a, ctx, b0, b1, lane, items); break;        \
+    case 2: tile_stream<T, V, 2, I64, 0, FS>(a, ctx, b0, b1, lane, items); break;        \
+    case 4: tile_stream<T, V, 4, I64, 0, FS>(a, ctx, b0, b1, lane, items); break;        \
+    default: tile_stream<T, V, 8, I64, 0, FS>(a, ctx, b0, b1, lane, items); break;       \
   }
 
 #define EB_DISPATCH_STREAM(I64)                                    \
@@ -50,9 +50,9 @@ namespace ebk {
 #define EB_DISPATCH_PIPE_T(T, V, I64, FS)                                                              \
   switch (fs.unroll) {                                                                                 \
     case 1:                                                                                            \
-    case 2: tile_stream<T, V, 2, I64, pipe_depth(2), FS>(ctx, b0, b1, lane, items, ring); break;       \
-    case 4: tile_stream<T, V, 4, I64, pipe_depth(4), FS>(ctx, b0, b1, lane, items, ring); break;       \
-    default: tile_stream<T, V, 8, I64, pipe_depth(8), FS>(ctx, b0, b1, lane, items, ring); break;      \
+    case 2: tile_stream<T, V, 2, I64, pipe_depth(2), FS>(a, ctx, b0, b1, lane, items, ring); break;       \
+    case 4: tile_stream<T, V, 4, I64, pipe_depth(4), FS>(a, ctx, b0, b1, lane, items, ring); break;       \
+    default: tile_stream<T, V, 8, I64, pipe_depth(8), FS>(a, ctx, b0, b1, lane, items, ring); break;      \
   }
 
 #define EB_DISPATCH_PIPE(I64)                                      \
@@ -79,11 +79,11 @@ namespace ebk {
   } else if (fs.kind == 3) {                                       \
     EB_DISPATCH_DTYPE_U4(tile_flat, true)                          \
   } else if (fs.kind == 4) {                                       \
-    if (fs.dtype == 1) tile_stream<__half, 8, 4, true>(ctx, b0, b1, lane, items); \
-    else tile_stream<float, 4, 4, true>(ctx, b0, b1, lane, items); \
+    if (fs.dtype == 1) tile_stream<__half, 8, 4, true>(a, ctx, b0, b1, lane, items); \
+    else tile_stream<float, 4, 4, true>(a, ctx, b0, b1, lane, items); \
   } else {                                                         \
-    if (fs.dtype == 1) tile_stream<__half, 8, 4, true, pipe_depth(4)>(ctx, b0, b1, lane, items, ring); \
-    else tile_stream<float, 4, 4, true, pipe_depth(4)>(ctx, b0, b1, lane, items, ring); \
+    if (fs.dtype == 1) tile_stream<__half, 8, 4, true, pipe_depth(4)>(a, ctx, b0, b1, lane, items, ring); \
+    else tile_stream<float, 4, 4, true, pipe_depth(4)>(a, ctx, b0, b1, lane, items, ring); \
   }
 
 #define EB_DISPATCH_KIND(I64)                                      \
@@ -103,11 +103,11 @@ namespace ebk {
 // One schedule at one unroll, both table dtypes, with and without the fast store.
 #define EB_ONE_WALK(U, D)                                                                              \
   if (fs.dtype == 1) {                                                                                 \
-    if (ctx.out_dt == 0 && ctx.out_vec == 2) tile_stream<__half, 8, U, false, D, true>(ctx, b0, b1, lane, items, ring);  \
-    else tile_stream<__half, 8, U, false, D, false>(ctx, b0, b1, lane, items, ring);                   \
+    if (ctx.out_dt == 0 && ctx.out_vec == 2) tile_stream<__half, 8, U, false, D, true>(a, ctx, b0, b1, lane, items, ring);  \
+    else tile_stream<__half, 8, U, false, D, false>(a, ctx, b0, b1, lane, items, ring);                   \
   } else {                                                                                             \
-    if (ctx.out_dt == 0 && ctx.out_vec >= 1) tile_stream<float, 4, U, false, D, true>(ctx, b0, b1, lane, items, ring);   \
-    else tile_stream<float, 4, U, false, D, false>(ctx, b0, b1, lane, items, ring);                    \
+    if (ctx.out_dt == 0 && ctx.out_vec >= 1) tile_stream<float, 4, U, false, D, true>(a, ctx, b0, b1, lane, items, ring);   \
+    else tile_stream<float, 4, U, false, D, false>(a, ctx, b0, b1, lane, items, ring);                    \
   }
 
 // KIND / UNROLL select what the kernel holds.  0 / 0: every schedule at every unroll (any assignment, any index
@@ -187,9 +187,7 @@ __global__ void __launch_bounds__(kCtaThreads, OCC) eb_fused_kernel(LaunchArgs a
     ctx.rows_per_peer = a.rows_per_peer;
     ctx.col_off = fs.col_off;
     ctx.status = &hdr->status;
-    ctx.long_list = reinterpret_cast<LongBagList*>(a.ws + L.long_list);
-    ctx.long_bytes = a.chunks > 0 ? 0 : a.long_bytes;  // in chunked order a chunk is complete when its tiles are
-    ctx.feat = f;
+    if (lane == 0) items[kBagItems - 1].x = f;  // for the rare hand-over of a long bag (tile_stream)
     ctx.dim = fs.dim;
     ctx.row_bytes = fs.row_bytes;
     ctx.lg_group = fs.lg_group;

@@ -43,9 +43,6 @@ struct TileCtx {
   int32_t out_dt;    // element type of the output: 0 = fp32, 1 = bfloat16, 2 = binary16
   int32_t es_shift;  // log2 of the output element size: 2 or 1
   uint32_t* status;
-  LongBagList* long_list;  // where bags too long for one warp are handed over (used when long_bytes > 0)
-  int64_t long_bytes;      // a bag gathering at least this many bytes is handed over; 0 = never
-  int32_t feat;            // the feature's number (for the hand-over)
   int32_t dim;
   int32_t row_bytes;
   int32_t lg_group;
@@ -191,14 +188,10 @@ __device__ __forceinline__ void store_vals(char* dstb, const float (&a)[V], int 
   } else {
     if constexpr (V == 8) {
       if (vec_ok == 2) {
-#ifdef EB_ROWS_INLINE
+        // no "memory" clobber: the walk's reads of the ring may move across this store; the one place that reads an
+        // output row back (the patch pass) sits behind a compiler barrier of its own
         asm volatile("st.global.cs.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "f"(a[0]), "f"(a[1]),
                      "f"(a[2]), "f"(a[3]), "f"(a[4]), "f"(a[5]), "f"(a[6]), "f"(a[7]));
-#else
-        asm volatile("st.global.cs.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "f"(a[0]), "f"(a[1]),
-                     "f"(a[2]), "f"(a[3]), "f"(a[4]), "f"(a[5]), "f"(a[6]), "f"(a[7])
-                     : "memory");
-#endif
         return;
       }
     }
@@ -734,7 +727,8 @@ __device__ __forceinline__ bool issue_rows(const TileCtx& c, const char* tcol, b
 // entries with valid indices (two uniform tests) issue their copies without any
 // predicate; only the ragged end of a piece and bad input take the checked path.
 // ---------------------------------------------------------------------------
-constexpr int kBagItems = 34;        // per-warp list of a chunk's non-empty bags: 32 + sentinel, padded
+constexpr int kBagItems = 34;        // per-warp list of a chunk's non-empty bags: 32 + sentinel; the last entry is
+                                     // never part of the list (the kernel keeps the tile's feature number there)
 constexpr int kNoEnd = 0x7fffffff;   // "this bag does not end inside my piece"
 
 
@@ -764,8 +758,8 @@ __device__ __forceinline__ void walk_store(char* dst, const float (&a)[V], int o
 }
 
 template <typename T, int V, int U, bool IDX64, int D = 0, bool FS = false>
-__device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_t b1, int lane, int2* items,
-                                            unsigned char* ring = nullptr) {
+__device__ __forceinline__ void tile_stream(const LaunchArgs& ka, const TileCtx& c, int64_t b0, int64_t b1, int lane,
+                                            int2* items, unsigned char* ring = nullptr) {
   static_assert(D == 0 || V * sizeof(T) == 16, "the ring holds 16-byte lane cells");
   using Ops = RowOps<T, V>;
   using IdxT = typename IdxOf<IDX64>::type;
@@ -779,75 +773,66 @@ __device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_
     const int cs = (xc * G + cl) * V;
     const bool col_ok = cs < c.dim;
     const char* tcol = c.table + (size_t)cs * sizeof(T);
+    // Chunks end at multiples of 32 bags (of the batch), so none straddles two ranks' rows in peer mode; a tile
+    // starts at a multiple of its own size, so only a tile narrower than 32 bags starts elsewhere.
     // 32-bit offsets: the boundaries of the next two chunks are fetched while this one is walked, so that a chunk
-    // starts without waiting for its offsets (lane i holds boundary pos0 + min(i, bags left))
+    // starts without waiting for its offsets (lane i holds boundary pos0 + min(i, bags of the chunk at pos0)).
     auto bounds_at = [&](int64_t pos0) -> int {
       if (pos0 > b1) return 0;
-      const int64_t cnt = (b1 - pos0) < 32 ? (b1 - pos0) : 32;
+      int64_t cnt = 32 - (pos0 & 31);
+      if (b1 - pos0 < cnt) cnt = b1 - pos0;
       return boundary32(c, pos0 + (lane < cnt ? lane : cnt));
     };
     int a_cur = 0, a_nxt = 0;
+    // Can a bag of this tile be long enough for eb_longbag_kernel?  Only if the whole tile is: one test per tile,
+    // kept as a predicate; everything else about long bags is looked up again in the rare branch that needs it.
+    bool maybe_long = false;
     if constexpr (!IDX64) {
       a_cur = bounds_at(b0);
-      a_nxt = bounds_at(b0 + 32);
+      a_nxt = bounds_at(b0 + (32 - (b0 & 31)));
+      if (ka.long_bytes > 0 && ka.chunks == 0 && c.nx == 1) {
+        const int64_t tile_entries = (int64_t)boundary32(c, b1) - (int64_t)boundary32(c, b0);
+        maybe_long = tile_entries * c.row_bytes >= ka.long_bytes;
+      }
     }
-    // a bag of this many entries or more is handed to eb_longbag_kernel (never, when the feature is off)
-    // (rows wider than one column pass are always pooled in place: every pass would have to take the same decision)
-    const int long_len = (IDX64 || c.long_bytes <= 0 || c.nx > 1) ? kNoEnd
-                         : (int)((c.long_bytes + c.row_bytes - 1) / c.row_bytes > 0x3fffffff
-                                     ? 0x3fffffff : (c.long_bytes + c.row_bytes - 1) / c.row_bytes);
     int nb = 0;
     for (int64_t bb = b0; bb < b1; bb += nb) {
-      // chunks start at multiples of 32 bags from b0, except right after a handed-over bag
-      nb = 32 - (int)((bb - b0) & 31);
+      nb = 32 - (int)(bb & 31);
       if (b1 - bb < nb) nb = (int)(b1 - bb);
       Chunk ch;
       if constexpr (!IDX64) {
-        const int a_fut = bounds_at(bb + 64);
-        ch = chunk_from32(c, a_cur, nb == 32 ? __shfl_sync(kFull, a_nxt, 0) : __shfl_sync(kFull, a_cur, 31), lane);
-#ifdef EB_NO_LONGBAG
-        const unsigned too_long = 0u;
-#else
-        const unsigned too_long = __ballot_sync(kFull, ch.hi - ch.lo >= long_len);
-#endif
-        if (too_long == 0u) {
+        if (!maybe_long) {
+          const int a_fut = bounds_at(bb + nb + 32);  // the chunk after the next one (which starts at a multiple of 32)
+          ch = chunk_from32(c, a_cur, nb == 32 ? __shfl_sync(kFull, a_nxt, 0) : __shfl_sync(kFull, a_cur, nb), lane);
           a_cur = a_nxt;
           a_nxt = a_fut;
         } else {
-          // rare: walk only the bags before the first long one now (or hand that bag over, when it comes first) and
-          // re-read the boundaries for the shortened schedule of chunks
-          const int p = __ffs(too_long) - 1;
-          bool handed = false;
-          if (p == 0) {
-            unsigned slot = 0;
-            if (lane == 0) slot = atomicAdd(&c.long_list->count, 1u);
-            slot = __shfl_sync(kFull, slot, 0);
-            handed = slot < (unsigned)kMaxLongBags;  // a full list takes no more: the bag is walked in place
-            if (handed && lane == 0) {
-              LongBag lb;
-              lb.feat = c.feat;
-              lb.pad_ = 0;
-              lb.bag = bb;
-              lb.begin = ch.e0 + ch.lo;
-              lb.end = ch.e0 + ch.hi;
-              c.long_list->item[slot] = lb;
+          // rare: a tile heavy enough to hold a long bag.  A chunk with such a bag is taken one bag at a time; the
+          // long ones go to eb_longbag_kernel's list (a full list takes no more: the bag is then walked here, alone)
+          ch = load_chunk<false>(c, bb, nb, lane);
+          const int64_t long_len = (ka.long_bytes + c.row_bytes - 1) / c.row_bytes;
+          if (__any_sync(kFull, (int64_t)(ch.hi - ch.lo) >= long_len)) {
+            nb = 1;
+            ch = load_chunk<false>(c, bb, 1, lane);
+            if ((int64_t)ch.n >= long_len) {
+              LongBagList* ll = reinterpret_cast<LongBagList*>(ka.ws + ws_layout(ka.num_features).long_list);
+              unsigned slot = 0;
+              if (lane == 0) slot = atomicAdd(&ll->count, 1u);
+              slot = __shfl_sync(kFull, slot, 0);
+              if (slot < (unsigned)kMaxLongBags) {
+                if (lane == 0) {
+                  LongBag lb;
+                  lb.feat = items[kBagItems - 1].x;  // the tile's feature, left there by the kernel
+                  lb.pad_ = 0;
+                  lb.bag = bb;
+                  lb.begin = ch.e0;
+                  lb.end = ch.e0 + ch.n;
+                  ll->item[slot] = lb;
+                }
+                continue;  // skipped here: eb_longbag_kernel pools it
+              }
             }
           }
-          if (p == 0 && handed) {
-            nb = 1;  // skipped here: eb_longbag_kernel pools it
-            a_cur = boundary32(c, bb + 1 + min(lane, min(31 - (int)((bb + 1 - b0) & 31), (int)(b1 - bb - 1))));
-            a_nxt = bounds_at(bb + 1 + (32 - ((bb + 1 - b0) & 31)));
-            continue;
-          }
-          const int keep = p == 0 ? 1 : p;  // a full list: the long bag is walked in place, alone
-          const int a_end = __shfl_sync(kFull, a_cur, keep);
-          ch = chunk_from32(c, lane <= keep ? a_cur : a_end, a_end, lane);
-          nb = keep;
-          const int64_t nbb = bb + nb;
-          int nnb = 32 - (int)((nbb - b0) & 31);
-          if (b1 - nbb < nnb) nnb = (int)(b1 - nbb);
-          a_cur = nbb < b1 ? boundary32(c, nbb + min(lane, nnb)) : 0;
-          a_nxt = bounds_at(nbb + nnb);
         }
       } else {
         ch = load_chunk<IDX64>(c, bb, nb, lane);
@@ -992,14 +977,9 @@ __device__ __forceinline__ void tile_stream(const TileCtx& c, int64_t b0, int64_
           if (cell_in == cell_end) cell_in = cell;
           if (m < 0) continue;
           cp_async_wait<D - 1>();
-#ifndef EB_ROWS_INLINE
-          typename Ops::Raw rows[U];
-#pragma unroll
-          for (int u = 0; u < U; ++u) rows[u] = *reinterpret_cast<const uint4*>(ring_lane + out_off + u * 512);
-#define EB_ROW(u) rows[u]
-#else
+          // rows are read out of the ring where they are added: holding all U of them in registers across the
+          // branch below costs more (spills at 3 CTAs per SM) than it saves
 #define EB_ROW(u) (*reinterpret_cast<const uint4*>(ring_lane + out_off + (u) * 512))
-#endif
           if (__all_sync(kFull, e + U < kend)) {
 #pragma unroll
             for (int u = 0; u < U; ++u) Ops::add(acc, EB_ROW(u));
