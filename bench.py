@@ -80,9 +80,10 @@ def parse_args():
     p.add_argument("--probe-exchange", action="store_true",
                    help="sharded path, peer exchange: also time the steps on a batch of empty bags, i.e. the same "
                         "stores to the same addresses with nothing gathered (the exchange alone)")
-    p.add_argument("--exchange", choices=["peer", "copy", "nccl"], default="",
-                   help="sharded path: fused peer-memory stores, pooling + copy-engine exchange, or pool + NCCL "
-                        "all-to-all + placement (default: copy on 8 GPUs, peer below)")
+    p.add_argument("--exchange", type=str, default="",
+                   help="sharded path, one or several of peer,copy,nccl (comma-separated): fused peer-memory stores, "
+                        "pooling + copy-engine exchange, or pool + NCCL all-to-all + placement (default: copy and peer "
+                        "on 8 GPUs, peer below)")
     p.add_argument("--out-dtype", choices=["f32", "bf16", "f16"], default="f32",
                    help="sharded path: element type of the exchanged rows")
     p.add_argument("--no-sharded", action="store_true", help="N > 1: skip the sharded sub-record")
@@ -440,8 +441,8 @@ def run_ours(args):
         lv, lo = raw[(K - 1) % nb]
         cols = np.concatenate([[0], np.cumsum([fs.dim for fs in cfg.features])])
         verified = synth.verify_sampled_cells(host_out.numpy(), cols, cfg, lv, lo, args.verify_cells, seed=11)
-        verified["tolerance_rel"] = 2e-3 if cfg.features[0].dtype == "f16" else 1e-5
-        verified["ok"] = bool(verified["max_rel_err"] <= verified["tolerance_rel"] and verified["empty_bags_exact_zero"])
+        verified["allowance"] = ("rel 2e-3" if cfg.features[0].dtype == "f16" else "rel 1e-5") + \
+                                " + abs 1e-6 + 2 ulp of the bag's sum of magnitudes (summation order)"
 
     # ---- timed region B: host buffers in, host result out ----
     # Two handles over the same tables alternate on two streams, so that step k + 1's upload overlaps step k's
@@ -565,7 +566,7 @@ def run_ours(args):
     # ---- N > 1: the table-wise sharded configuration on the same GPUs (frees this workload's tables first) ----
     sharded = None
     if world > 1 and not args.no_sharded and args.workload == "cfg3" and args.row_scale == 1.0 and not args.batch:
-        mod_b = lanes = None
+        mod_b = lanes = lanes_f32 = out_s = e2e_steps = None
         del tables, mod, dev_v, dev_o, out
         import gc
 
@@ -574,7 +575,7 @@ def run_ours(args):
         cap = int(torch.cuda.mem_get_info(dev)[1] * 0.88)
         try:
             sharded = measure_sharded(args, dev, world, rank, default_exchanges(args, world), sharded_row_scale(world, cap),
-                                      max(10, min(K, 20)), tune=True)
+                                      max(10, min(K, 20)), tune=True, probe=True)
         except Exception as exc:
             sharded = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
 
@@ -807,7 +808,12 @@ def measure_sharded(args, dev, world, rank, exchanges, row_scale, steps, tune, n
     result["one_gpu_equivalent_ms"] = sum(alone_all)
     result["algorithmic_bytes_per_step"] = sum(float(g[1]) for g in gathered)
 
-    for exchange in exchanges:
+    for entry in exchanges:
+        exchange = entry.split(":")[0]
+        if ":" in entry:
+            odt = {"bf16": torch.bfloat16, "f16": torch.float16}[entry.split(":")[1]]
+        else:
+            odt = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[out_dtype]
         chunks = args.chunks or (8 if exchange == "copy" else 4)
         mod = ShardedFeatEmbed(rank, world, owner, dims, local_tables=tables, device=dev, chunks=chunks,
                                exchange=exchange, out_dtype=odt if exchange != "nccl" else torch.float32)
@@ -816,7 +822,10 @@ def measure_sharded(args, dev, world, rank, exchanges, row_scale, steps, tune, n
             mod.local.set_schedules(scheds, occupancy=occ)
         out_buf = torch.empty((B // world, cfg.output_units), dtype=torch.float32, device=dev) if exchange == "nccl" else None
         run_step = (lambda v, o: mod(v, o, out=out_buf)) if exchange == "nccl" else (lambda v, o: mod(v, o))
-        rec = {"chunks": chunks if exchange != "peer" else 1}
+        rec = {"chunks": chunks if exchange != "peer" else 1,
+               "row_dtype": "f32" if (exchange == "nccl" or odt == torch.float32) else ("bf16" if odt == torch.bfloat16 else "f16")}
+        sent = max(summ["exchange_per_rank"]) * (1.0 if rec["row_dtype"] == "f32" else 0.5)
+        rec["bytes_sent_per_rank_per_step"] = int(sent)
         try:
             if mod.local is not None:
                 mod.local.kernel_timing(True)
@@ -844,7 +853,7 @@ def measure_sharded(args, dev, world, rank, exchanges, row_scale, steps, tune, n
                 stats = torch.tensor([t3], dtype=torch.float64, device=dev)
                 dist.all_reduce(stats, op=dist.ReduceOp.MAX)
                 rec["exchange_alone_ms_per_step"] = float(stats[0]) / steps * 1e3
-                rec["exchange_alone_gbs_per_rank"] = result["exchange_bytes_sent_per_rank_per_step"] / (float(stats[0]) / steps) / 1e9
+                rec["exchange_alone_gbs_per_rank"] = sent / (float(stats[0]) / steps) / 1e9
             if e2e:
                 host_out = torch.empty((B // world, cfg.output_units), dtype=torch.float32 if exchange == "nccl" else odt).pin_memory()
 
@@ -863,21 +872,26 @@ def measure_sharded(args, dev, world, rank, exchanges, row_scale, steps, tune, n
                 rec["d2h_bytes_per_step"] = int(host_out.numel() * host_out.element_size())
         except Exception as exc:  # an exchange the box cannot run (for example no stream memory operations): say so
             rec["unavailable"] = f"{type(exc).__name__}: {exc}"[:300]
-        result["exchanges"][exchange] = rec
+        result["exchanges"][entry] = rec
         barrier()
         if exchange != "nccl":
             mod.close()
         del mod
         torch.cuda.empty_cache()
-    ok = {k: v for k, v in result["exchanges"].items() if "ms_per_step" in v}
+    ok = {k: v for k, v in result["exchanges"].items() if "ms_per_step" in v and v.get("row_dtype") == "f32"}
     result["best_exchange"] = min(ok, key=lambda k: ok[k]["ms_per_step"]) if ok else None
     return result
 
 
 def default_exchanges(args, world):
     if args.exchange:
-        return [args.exchange]
-    return ["copy", "peer"] if world >= 8 else ["peer"]
+        names = [x for x in args.exchange.split(",") if x]
+        for x in names:
+            if x.split(":")[0] not in ("peer", "copy", "nccl") or x.split(":")[-1] not in ("peer", "copy", "nccl", "bf16", "f16"):
+                raise SystemExit(f"unknown exchange {x!r}")
+        return names
+    # fp32 rows are the contract; the bf16 entry shows what a consumer that casts anyway (RecomModel in bf16) gets
+    return ["peer", "copy", "peer:bf16"] if world >= 8 else ["peer", "peer:bf16"]
 
 
 def run_sharded(args):

@@ -320,15 +320,19 @@ int eb_set_output_dtype(eb_handle* h, int out_dtype);
  * sample b belongs to destination rank b / (batch / world), and piece k holds
  * rows [k, k + 1) * batch / (world * chunks) of every destination.  As soon as
  * the kernel has finished a piece (a device flag the kernel raises; the copy
- * stream waits for it with a stream memory operation, the host is not
- * involved), `copy_stream` copies the piece's rows to every destination:
- * rank d receives them in peer_out[d] ([batch / world, out_ld] elements, THIS
- * process's pointer to rank d's matrix, see eb_peer_open) at columns
- * [out_col, out_col + output units), rows in batch order.  The copies of piece
- * k run while piece k + 1 is pooled.  A kernel launched right after the
+ * streams wait for it with a stream memory operation, the host is not
+ * involved), the `copy_streams` (1 to 16 streams of the caller; destinations
+ * are dealt over them so that several copy engines work at once) copy the
+ * piece's rows to every other rank: rank d receives them in peer_out[d]
+ * ([batch / world, out_ld] elements, THIS process's pointer to rank d's
+ * matrix, see eb_peer_open) at columns [out_col, out_col + output units), rows
+ * in batch order.  This rank's own samples never enter the send buffer: the
+ * kernel stores them straight into peer_out[rank].  The copies of piece k run
+ * while piece k + 1 is pooled.  A kernel launched right after the
  * pooling kernel raises every flag, so the copy stream can never wait longer
- * than the pooling runs.  The caller orders consumers after all ranks' copy
- * streams, and must not reuse `send` before `copy_stream` is done with it.
+ * than the pooling runs.  The caller orders consumers after `stream` (own
+ * samples) and all ranks' copy streams, and must not reuse `send` before the
+ * copy streams are done with it.
  * batch must be a multiple of world * chunks; world <= 16, chunks <= 64.
  * The flags live in `workspace` and count calls: zero-fill a workspace once
  * before its first use here.
@@ -338,7 +342,8 @@ int eb_forward_exchange(eb_handle* h, int64_t batch, const void* const* values_p
                         const void* const* offsets_ptrs, const int64_t* nnz, int index_dtype,
                         int offsets_have_end, float* send, int64_t send_ld, float* const* peer_out,
                         int world, int rank, int64_t out_ld, int64_t out_col, int chunks,
-                        void* workspace, size_t workspace_bytes, void* stream, void* copy_stream);
+                        void* workspace, size_t workspace_bytes, void* stream,
+                        void* const* copy_streams, int num_copy_streams);
 
 /*
  * Overlap of the two pooling kernels (no counterpart in the reference, whose

@@ -98,7 +98,7 @@ PROTOTYPES = {
     "eb_forward_exchange": (C.c_int, [C.c_void_p, C.c_int64, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
                                       C.POINTER(C.c_int64), C.c_int, C.c_int, C.c_void_p, C.c_int64,
                                       C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int,
-                                      C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]),
+                                      C.c_void_p, C.c_size_t, C.c_void_p, C.POINTER(C.c_void_p), C.c_int]),
     "eb_last_error": (C.c_char_p, []),
     "eb_version": (C.c_char_p, []),
 }

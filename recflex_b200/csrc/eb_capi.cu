@@ -522,11 +522,14 @@ StreamWaitValue32 stream_wait_value32() {
 int eb_forward_exchange(eb_handle* h, int64_t batch, const void* const* values_ptrs, const void* const* offsets_ptrs,
                         const int64_t* nnz, int index_dtype, int offsets_have_end, float* send, int64_t send_ld,
                         float* const* peer_out, int world, int rank, int64_t out_ld, int64_t out_col, int chunks,
-                        void* workspace, size_t workspace_bytes, void* stream, void* copy_stream) {
+                        void* workspace, size_t workspace_bytes, void* stream, void* const* copy_streams,
+                        int num_copy_streams) {
   if (world < 1 || world > kMaxPeers) return fail(EB_ERR_INVALID_ARG, "world must be 1..%d (got %d)", kMaxPeers, world);
   if (rank < 0 || rank >= world) return fail(EB_ERR_INVALID_ARG, "rank %d outside [0, %d)", rank, world);
   if (chunks < 1 || chunks > kMaxChunks) return fail(EB_ERR_INVALID_ARG, "chunks must be 1..%d (got %d)", kMaxChunks, chunks);
   if (!peer_out) return fail(EB_ERR_INVALID_ARG, "null peer_out");
+  if (!copy_streams || num_copy_streams < 1 || num_copy_streams > kMaxPeers)
+    return fail(EB_ERR_INVALID_ARG, "between 1 and %d copy streams are needed", kMaxPeers);
   int rc = check_forward_common(h, batch, index_dtype, send, send_ld, workspace, workspace_bytes);
   if (rc != EB_OK) return rc;
   if (batch == 0) return EB_OK;
@@ -540,7 +543,7 @@ int eb_forward_exchange(eb_handle* h, int64_t batch, const void* const* values_p
   StreamWaitValue32 wait32 = stream_wait_value32();
   if (!wait32) return fail(EB_ERR_UNSUPPORTED, "the driver offers no cuStreamWaitValue32 (stream memory operations)");
   DeviceGuard guard(h->device);
-  cudaStream_t st = static_cast<cudaStream_t>(stream), cst = static_cast<cudaStream_t>(copy_stream);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
   rc = upload_dyn(h, batch, values_ptrs, offsets_ptrs, nnz, offsets_have_end, workspace, st);
   if (rc != EB_OK) return rc;
   LaunchArgs a = make_args(h, batch, index_dtype, offsets_have_end, send, send_ld, workspace);
@@ -549,17 +552,28 @@ int eb_forward_exchange(eb_handle* h, int64_t batch, const void* const* values_p
   a.chunk_rows = a.dest_rows / chunks;
   if (++h->epoch == 0) h->epoch = 1;  // a fresh workspace holds zeros: epoch 0 is never waited for
   a.epoch = h->epoch;
+  const size_t es = out_elem_bytes(h);
+  a.own_out = peer_out[rank];  // this rank's own samples skip the send buffer
+  a.own_ld = out_ld;
+  a.own_col = (int32_t)out_col;
+  a.own_rank = rank;
+  a.own_vec = out_vec_of(peer_out[rank], out_ld, es);
   rc = run(h, a, false, st);
   if (rc != EB_OK) return rc;
-  // copy stream: as soon as chunk k is published, its rows leave for every destination
-  const size_t es = out_elem_bytes(h);
+  // copy streams: as soon as chunk k is published, its rows leave for every other rank; destination i hops to the
+  // right of this rank uses stream (i - 1) mod n, so several copy engines work at once
   const ChunkSync* cs = reinterpret_cast<const ChunkSync*>(static_cast<char*>(workspace) + ws_layout(h->num_features).chunk_sync);
   const size_t width = (size_t)h->units * es;
+  const int ns = num_copy_streams < world - 1 ? num_copy_streams : (world > 1 ? world - 1 : 1);
   for (int k = 0; k < chunks; ++k) {
-    const int wrc = wait32(cst, (unsigned long long)reinterpret_cast<uintptr_t>(&cs->flag[k]), a.epoch, 0u /* >= */);
-    if (wrc != 0) return fail(EB_ERR_CUDA, "cuStreamWaitValue32 failed with driver error %d", wrc);
-    for (int i = 1; i <= world; ++i) {
-      const int d = (rank + i) % world;  // every rank starts with its right-hand neighbour; its own rows go last
+    for (int j = 0; j < ns && world > 1; ++j) {
+      const int wrc = wait32(static_cast<cudaStream_t>(copy_streams[j]),
+                             (unsigned long long)reinterpret_cast<uintptr_t>(&cs->flag[k]), a.epoch, 0u /* >= */);
+      if (wrc != 0) return fail(EB_ERR_CUDA, "cuStreamWaitValue32 failed with driver error %d", wrc);
+    }
+    for (int i = 1; i < world; ++i) {
+      const int d = (rank + i) % world;
+      cudaStream_t cst = static_cast<cudaStream_t>(copy_streams[(i - 1) % ns]);
       const char* src = reinterpret_cast<const char*>(send) + ((size_t)d * a.dest_rows + (size_t)k * a.chunk_rows) * send_ld * es;
       char* dst = reinterpret_cast<char*>(peer_out[d]) + ((size_t)k * a.chunk_rows * out_ld + out_col) * es;
       EB_CUDA(cudaMemcpy2DAsync(dst, (size_t)out_ld * es, src, (size_t)send_ld * es, width, (size_t)a.chunk_rows,

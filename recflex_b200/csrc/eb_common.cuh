@@ -164,6 +164,14 @@ struct LaunchArgs {
   uint32_t epoch;         // value written to a chunk's flag when its last tile is done
   int64_t chunk_rows;
   int64_t dest_rows;
+  // chunked order: the rows of destination own_rank (this rank's own samples) skip the send buffer and go straight
+  // to own_out ([dest_rows, own_ld] elements) at columns own_col + the feature's column; null = no such shortcut
+  float* own_out;
+  int64_t own_ld;
+  int32_t own_col;
+  int32_t own_rank;
+  int32_t own_vec;        // like out_vec, for own_out
+  int32_t pad2_;
   // peer mode (rows_per_peer > 0): sample b is stored to peer_out[b / rows_per_peer], row b % rows_per_peer
   int64_t rows_per_peer;
   float* peer_out[kMaxPeers];

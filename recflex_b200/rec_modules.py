@@ -303,10 +303,11 @@ class FeatEmbed(nn.Module):
 
     def forward_exchange(self, values: Sequence[torch.Tensor], offsets: Sequence[torch.Tensor], send: torch.Tensor,
                          peer_ptrs: Sequence[int], rank: int, out_ld: int, out_col: int, chunks: int,
-                         copy_stream: torch.cuda.Stream) -> None:
+                         copy_streams: Sequence[torch.cuda.Stream]) -> None:
         """Pooling + copy-engine exchange (see eb_forward_exchange in include/recflex_b200.h): pools the whole batch
-        into `send` ([batch, >= output_units], this module's output dtype) piece by piece and lets `copy_stream`
-        ship every finished piece to the ranks' matrices `peer_ptrs` at columns [out_col, out_col + output_units)."""
+        into `send` ([batch, >= output_units], this module's output dtype) piece by piece and lets `copy_streams`
+        ship every finished piece to the other ranks' matrices `peer_ptrs` at columns [out_col, out_col +
+        output_units); this rank's own samples are stored straight into peer_ptrs[rank] by the kernel."""
         idt, batch, vp, op, nnz = self._feature_pointers(values, offsets)
         send = self._check_out(send, batch)
         W = len(peer_ptrs)
@@ -314,7 +315,8 @@ class FeatEmbed(nn.Module):
         _lib.check(self._lib.eb_forward_exchange(self._h, batch, vp, op, nnz, idt, 1, C.c_void_p(send.data_ptr()),
                                                  send.stride(0), pp, W, int(rank), int(out_ld), int(out_col),
                                                  int(chunks), C.c_void_p(self._ws_ptr), self._ws_bytes, self._stream(),
-                                                 C.c_void_p(copy_stream.cuda_stream)))
+                                                 (C.c_void_p * len(copy_streams))(*[s.cuda_stream for s in copy_streams]),
+                                                 len(copy_streams)))
 
     def forward_packed(self, values: torch.Tensor, offsets: torch.Tensor, out: Optional[torch.Tensor] = None):
         """Same forward for one packed batch: `values` = all features' indices back to back,

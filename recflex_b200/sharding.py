@@ -231,6 +231,7 @@ class ShardedFeatEmbed:
             self.local = FeatEmbed(self.device, embed_tables=local_tables) if local_tables else None
             self._lib = _lib.load()
             self._comm = torch.cuda.Stream(device=self.device)
+            self._copy_streams = [torch.cuda.Stream(device=self.device) for _ in range(min(4, max(1, world - 1)))]
         else:
             self.device = torch.device(device) if device is not None else torch.device("cpu")
         self._segs = {}      # rows per chunk -> device descriptor tensor for the placement kernel
@@ -426,10 +427,11 @@ class ShardedFeatEmbed:
             cur.wait_event(self._copy_done[b])  # the copies that read this send buffer two calls ago are done
         if self.local is not None:
             self.local.forward_exchange(values, offsets, self._send[b], ptrs[b], self.rank, self.units,
-                                        self.block_col[self.rank], Cn, self._comm)
+                                        self.block_col[self.rank], Cn, self._copy_streams)
         with torch.cuda.stream(self._comm):
-            if self.local is None:
-                self._comm.wait_stream(cur)
+            self._comm.wait_stream(cur)  # the kernel stores this rank's own samples itself
+            for cs in self._copy_streams:
+                self._comm.wait_stream(cs)
             dist.all_reduce(self._flag, group=self.group)  # after it, every rank's copies into my matrix are complete
             done = torch.cuda.Event()
             done.record()

@@ -287,9 +287,10 @@ def algorithmic_bytes(cfg: ModelConfig, offsets: Sequence[np.ndarray], index_byt
 def sampled_cells(cfg: ModelConfig, values: Sequence[np.ndarray], offsets: Sequence[np.ndarray], n: int,
                   seed: int = 0, features: Optional[Sequence[int]] = None):
     """`n` random (sample, feature) cells of one batch with what they must pool to: yields
-    (sample, position of the feature in `features`, expected fp32 vector).  The expected vector is the float64 sum
-    of the bag's rows regenerated from the counter-based weights (no table is stored), rounded to fp32; an empty
-    bag gives zeros.  `values` / `offsets` are per-feature lists aligned with `features` (default: all)."""
+    (sample, position of the feature in `features`, expected fp32 vector, sum of magnitudes).  The expected vector is
+    the float64 sum of the bag's rows regenerated from the counter-based weights (no table is stored), rounded to
+    fp32; an empty bag gives zeros.  `values` / `offsets` are per-feature lists aligned with `features` (default:
+    all)."""
     feats = list(range(len(cfg.features))) if features is None else list(features)
     rng = np.random.default_rng(seed)
     batch = len(offsets[0]) - 1
@@ -299,28 +300,35 @@ def sampled_cells(cfg: ModelConfig, values: Sequence[np.ndarray], offsets: Seque
         fs = cfg.features[feats[k]]
         idx = np.asarray(values[k][int(offsets[k][b]):int(offsets[k][b + 1])], dtype=np.int64)
         if len(idx) == 0:
-            yield b, k, np.zeros(fs.dim, dtype=np.float32)
+            yield b, k, np.zeros(fs.dim, dtype=np.float32), np.zeros(fs.dim, dtype=np.float64)
             continue
         uniq, inv = np.unique(idx, return_inverse=True)
-        rows = synth_rows(fs.seed, uniq, fs.dim, fs.dtype).astype(np.float64)
-        yield b, k, rows[inv].sum(axis=0).astype(np.float32)
+        rows = synth_rows(fs.seed, uniq, fs.dim, fs.dtype).astype(np.float64)[inv]
+        yield b, k, rows.sum(axis=0).astype(np.float32), np.abs(rows).sum(axis=0)
 
 
 def verify_sampled_cells(out_host: np.ndarray, first_cols: Sequence[int], cfg: ModelConfig, values, offsets, n: int,
                          seed: int = 0, features: Optional[Sequence[int]] = None) -> dict:
     """Compare `n` sampled cells of a pooled output (host array [batch, units]; feature k of `features` starts at
-    column first_cols[k]) with sums of regenerated rows.  Returns the cell count, the largest relative error
-    (|got - expect| / max(|expect|, 1e-3)) and whether every sampled empty bag was exactly zero."""
+    column first_cols[k]) with sums of regenerated rows.  Each element is allowed the benchmark's tolerance (fp32
+    tables: rel 1e-5 + abs 1e-6; fp16 tables: rel 2e-3 + abs 1e-6) plus two units in the last place of the bag's sum of
+    magnitudes (2 x 2^-24 x sum |row|: what two correct fp32 summations in different orders may differ by, which
+    matters for bags of a thousand rows).  Returns the cell count, the worst error as a multiple of its allowance,
+    the worst plain relative error, and whether every sampled empty bag was exactly zero."""
     feats = list(range(len(cfg.features))) if features is None else list(features)
-    worst, zeros_ok = 0.0, True
-    for b, k, expect in sampled_cells(cfg, values, offsets, n, seed, features):
-        dim = cfg.features[feats[k]].dim
-        got = out_host[b, first_cols[k]:first_cols[k] + dim]
+    worst, worst_rel, zeros_ok = 0.0, 0.0, True
+    for b, k, expect, mags in sampled_cells(cfg, values, offsets, n, seed, features):
+        fs = cfg.features[feats[k]]
+        got = out_host[b, first_cols[k]:first_cols[k] + fs.dim].astype(np.float64)
         if int(offsets[k][b]) == int(offsets[k][b + 1]):
             zeros_ok = zeros_ok and bool(np.all(got == 0.0))
-        err = np.abs(got.astype(np.float64) - expect) / np.maximum(np.abs(expect), 1e-3)
-        worst = max(worst, float(err.max()))
-    return {"cells": n, "max_rel_err": worst, "empty_bags_exact_zero": zeros_ok}
+        rtol = 2e-3 if fs.dtype == "f16" else 1e-5
+        err = np.abs(got - expect)
+        allowed = rtol * np.abs(expect) + 1e-6 + 2.0 * 2.0 ** -24 * mags
+        worst = max(worst, float((err / allowed).max()))
+        worst_rel = max(worst_rel, float((err / np.maximum(np.abs(expect), 1e-3)).max()))
+    return {"cells": n, "max_err_over_allowance": worst, "max_rel_err": worst_rel, "empty_bags_exact_zero": zeros_ok,
+            "ok": bool(worst <= 1.0 and zeros_ok)}
 
 
 def make_tables_numpy(cfg: ModelConfig) -> List[np.ndarray]:

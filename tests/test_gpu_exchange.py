@@ -42,7 +42,7 @@ def test_copy_engine_exchange_on_one_device(kind, chunks):
     B, units = cfg.batch, cfg.output_units
     results = [torch.full((rows, units), float("nan"), device="cuda:0") for _ in range(world)]
     ptrs = [t.data_ptr() for t in results]
-    copy_stream = torch.cuda.Stream()
+    copy_streams = [torch.cuda.Stream() for _ in range(2)]
     column_of, block = [0] * len(cfg.features), 0
     for rank in range(world):
         local, mod = _rank_module(cfg, tables, owner, rank, kind)
@@ -50,8 +50,9 @@ def test_copy_engine_exchange_on_one_device(kind, chunks):
         dv = [torch.from_numpy(values[f]).cuda() for f in local]
         do = [torch.from_numpy(offsets[f]).cuda() for f in local]
         for _ in range(2):  # the second call meets the flags the first one left raised
-            mod.forward_exchange(dv, do, send, ptrs, rank, units, block, chunks, copy_stream)
-            torch.cuda.current_stream().wait_stream(copy_stream)
+            mod.forward_exchange(dv, do, send, ptrs, rank, units, block, chunks, copy_streams)
+            for cs in copy_streams:
+                torch.cuda.current_stream().wait_stream(cs)
         torch.cuda.synchronize()
         mod.check_status()
         c = block
@@ -95,4 +96,4 @@ def test_chunked_order_rejects_batches_it_cannot_split():
     from recflex_b200._lib import EbError
 
     with pytest.raises(EbError):  # 128 samples do not split into 2 ranks x 3 pieces
-        mod.forward_exchange(dv, do, send, [res.data_ptr()] * 2, 0, cfg.output_units, 0, 3, torch.cuda.Stream())
+        mod.forward_exchange(dv, do, send, [res.data_ptr()] * 2, 0, cfg.output_units, 0, 3, [torch.cuda.Stream()])

@@ -98,7 +98,7 @@ def test_full_size_sampled_against_oracle_and_across_schedules(cfg3_batch):
         del other
     cols = np.concatenate([[0], np.cumsum([fs.dim for fs in cfg.features])])
     host = out.cpu().numpy()
-    for b, f, expect64 in synth.sampled_cells(cfg, values, offsets, 3000, seed=7):
+    for b, f, expect64, _ in synth.sampled_cells(cfg, values, offsets, 3000, seed=7):
         fs = cfg.features[f]
         got = host[b, cols[f]:cols[f + 1]]
         idx = values[f][offsets[f][b]:offsets[f][b + 1]].astype(np.int64)
