@@ -344,6 +344,38 @@ def run_ours(args):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
+    # every tensor of the replicated workload lives (and dies) inside measure_replicated: the sharded configuration
+    # below needs the memory
+    line = measure_replicated(args, dev, world, rank, local_rank)
+    if world > 1 and not args.no_sharded and args.workload == "cfg3" and args.row_scale == 1.0 and not args.batch:
+        import gc
+
+        gc.collect()
+        torch.cuda.empty_cache()
+        cap = int(torch.cuda.mem_get_info(dev)[1] * 0.88)
+        try:
+            sharded = measure_sharded(args, dev, world, rank, default_exchanges(args, world), sharded_row_scale(world, cap),
+                                      max(10, min(args.steps, 20)), tune=True, probe=True)
+        except Exception as exc:
+            sharded = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+        if line is not None:
+            line["sharded"] = sharded
+    if line is not None:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def measure_replicated(args, dev, world, rank, local_rank):
+    """The replicated-tables workload on this rank's GPU: resident-input timing, host-buffer timing (fp32 and bf16
+    rows), the self-check, strong scaling, the end-to-end model; returns the JSON line (rank 0) or None."""
+    import torch
+    import torch.distributed as dist
+
+    from recflex_b200 import _lib, synth
+    from recflex_b200.rec_modules import FeatEmbed, Schedule
+
     def barrier():
         if world > 1:
             dist.barrier()
@@ -563,22 +595,6 @@ def run_ours(args):
         del per_feature
         torch.cuda.empty_cache()
 
-    # ---- N > 1: the table-wise sharded configuration on the same GPUs (frees this workload's tables first) ----
-    sharded = None
-    if world > 1 and not args.no_sharded and args.workload == "cfg3" and args.row_scale == 1.0 and not args.batch:
-        mod_b = lanes = lanes_f32 = out_s = e2e_steps = None
-        del tables, mod, dev_v, dev_o, out
-        import gc
-
-        gc.collect()
-        torch.cuda.empty_cache()
-        cap = int(torch.cuda.mem_get_info(dev)[1] * 0.88)
-        try:
-            sharded = measure_sharded(args, dev, world, rank, default_exchanges(args, world), sharded_row_scale(world, cap),
-                                      max(10, min(K, 20)), tune=True, probe=True)
-        except Exception as exc:
-            sharded = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
-
     if rank == 0:
         peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
         if os.path.exists(peaks_path):
@@ -600,8 +616,8 @@ def run_ours(args):
             "metric": METRIC, "value": world * K * B / t_dev, "unit": UNIT, "n_gpus": world, "steps": K,
             "warmup": max(3, args.warmup), "ms_per_step": t_dev / K * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {**workload_config(cfg, args), "schedules": sched_note, "occupancy": occupancy,
-                       "index_dtype": "int32"},
+            "config": workload_config(cfg, args),  # the same keys and values as the reference arm's line
+            "tuning": {"schedules": sched_note, "occupancy": occupancy, "index_dtype": "int32"},
             "roofline": {
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak if achieved else None, "traffic": traffic,
@@ -631,8 +647,6 @@ def run_ours(args):
                                       "batch / (N x time of the split step)"}
         if recom:
             line["recom_model"] = recom
-        if sharded is not None:
-            line["sharded"] = sharded
         if world == 1 and args.workload in ("cfg1", "cfg2", "cfg5") and args.row_scale == 1.0:
             try:
                 rt = time_reference_gpu_templates(cfg, tables, first[0], first[1], dev)
@@ -643,10 +657,8 @@ def run_ours(args):
         if world == 1 and not args.no_cpu_baseline:
             res = time_cpu(cfg, first[0], first[1], args.cpu_seconds)
             line["cpu_baseline"] = {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")}
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        return line
+    return None
 
 
 def plan_cfg_shards(cfg, world, cap):

@@ -80,11 +80,13 @@ extern "C" {
  *                   atomics nor scans in the inner loop.
  *   EB_SCHED_PIPE   EB_SCHED_STREAM with the rows in flight kept in a per-warp
  *                   shared-memory ring filled by per-lane cp.async copies
- *                   (unroll 2 / 4 / 8 -> 4 / 3 / 2 macro-steps deep) instead of
- *                   in registers: more bytes in flight per lane, fewer
- *                   registers; costs 64 KB of shared memory per CTA, so at most
- *                   3 CTAs per SM run (a higher occupancy setting is honoured
- *                   only up to what fits).  No counterpart in the reference.
+ *                   (unroll 2 / 4 / 6 / 8 -> 4 / 3 / 2 / 2 macro-steps deep:
+ *                   8, 12, 12 or 16 rows per lane in flight) instead of in
+ *                   registers: more bytes in flight per lane, fewer registers;
+ *                   costs 48 KB (64 KB at unroll 8) of shared memory per CTA, so
+ *                   at most 4 (3) CTAs per SM run (a higher occupancy setting is
+ *                   honoured only up to what fits).  No counterpart in the
+ *                   reference.
  *   EB_SCHED_AUTO   the library's default: EB_SCHED_STREAM with four rows in flight, whatever the feature
  *                   looks like.  Choosing per feature from dim, dtype and bag lengths is the tuner's job
  *                   (recflex_b200/tuning.py), which replaces this default.
@@ -102,7 +104,7 @@ typedef struct eb_handle eb_handle;
  * pair (RecFlex/code_emitter/schedule_base.py:54-87). */
 typedef struct eb_schedule {
   int32_t kind;          /* EB_SCHED_* */
-  int32_t unroll;        /* rows kept in flight per lane: 1, 2, 4 or 8 (0 = auto); batches with 64-bit indices always run at 4 */
+  int32_t unroll;        /* rows per lane and macro-step: 1, 2, 4 or 8, or 6 with EB_SCHED_PIPE (0 = auto); batches with 64-bit indices always run at 4 */
   int32_t vec_bytes;     /* bytes per lane per row load: 16 (0 = auto; rows that are not 16-byte multiples use the element-wise fallback) */
   int32_t bags_per_tile; /* bags bound to one warp per tile; 0 = chosen on the device from the batch's mean bag length */
 } eb_schedule;

@@ -114,8 +114,10 @@ eb_schedule resolve(const eb_schedule& in) {
 int check_schedule(const eb_schedule& s, int f) {
   if (s.kind < EB_SCHED_AUTO || s.kind > EB_SCHED_PIPE)
     return fail(EB_ERR_INVALID_ARG, "feature %d: unknown schedule kind %d", f, s.kind);
-  if (!(s.unroll == 0 || s.unroll == 1 || s.unroll == 2 || s.unroll == 4 || s.unroll == 8))
-    return fail(EB_ERR_INVALID_ARG, "feature %d: unroll must be 0, 1, 2, 4 or 8 (got %d)", f, s.unroll);
+  if (!(s.unroll == 0 || s.unroll == 1 || s.unroll == 2 || s.unroll == 4 || s.unroll == 8 ||
+        (s.unroll == 6 && s.kind == EB_SCHED_PIPE)))
+    return fail(EB_ERR_INVALID_ARG, "feature %d: unroll must be 0, 1, 2, 4 or 8, or 6 with EB_SCHED_PIPE (got %d)", f,
+                s.unroll);
   if (!(s.vec_bytes == 0 || s.vec_bytes == 16))
     return fail(EB_ERR_INVALID_ARG, "feature %d: vec_bytes must be 0 or 16 (got %d)", f, s.vec_bytes);
   if (s.bags_per_tile < 0 || s.bags_per_tile > 1024 || (s.bags_per_tile & (s.bags_per_tile - 1)))
@@ -369,7 +371,10 @@ int eb_set_schedules(eb_handle* h, const eb_schedule* per_feature, int occupancy
     for (int f = 0; f < h->num_features; ++f) {
       h->sched[f] = resolve(per_feature[f]);
       // the ring holds 16-byte lane cells: element-wise fallback rows keep the register walk
-      if (h->sched[f].kind == EB_SCHED_PIPE && !h->feats[f].vec) h->sched[f].kind = EB_SCHED_STREAM;
+      if (h->sched[f].kind == EB_SCHED_PIPE && !h->feats[f].vec) {
+        h->sched[f].kind = EB_SCHED_STREAM;
+        if (h->sched[f].unroll == 6) h->sched[f].unroll = 4;
+      }
       apply_schedule(h->feats[f], h->sched[f]);
       if (h->sched[f].kind == EB_SCHED_PIPE) {
         const int need = pipe_cells(h->sched[f].unroll);
@@ -391,7 +396,8 @@ int eb_set_schedules(eb_handle* h, const eb_schedule* per_feature, int occupancy
     }
     const bool family = kind == EB_SCHED_STREAM || kind == EB_SCHED_PIPE;
     h->only_kind = family ? kind : 0;
-    h->only_unroll = (family && (unroll == 2 || unroll == 4 || unroll == 8)) ? unroll : 0;
+    h->only_unroll = (family && (unroll == 2 || unroll == 4 || unroll == 8 || (unroll == 6 && kind == EB_SCHED_PIPE)))
+                         ? unroll : 0;
     DeviceGuard guard(h->device);
     const int rc = upload_feats(h);
     if (rc != EB_OK) return rc;

@@ -22,10 +22,10 @@ constexpr int kPipeMaxCells = 16;        // unroll x stages of the deepest pipel
 // Macro-steps the pipelined schedule keeps in flight, by unroll (rows per macro-step); the ring holds unroll x depth
 // cells of 512 bytes per warp.  Batches with 64-bit indices always run the unroll-4 variant.
 __host__ __device__ constexpr inline int pipe_depth(int unroll) {
-  return unroll <= 2 ? EB_PIPE_D2 : (unroll == 4 ? EB_PIPE_D4 : EB_PIPE_D8);
+  return unroll <= 2 ? EB_PIPE_D2 : (unroll == 4 ? EB_PIPE_D4 : EB_PIPE_D8);  // 6 and 8: two macro-steps
 }
 __host__ __device__ constexpr inline int pipe_cells(int unroll) {
-  const int u = unroll <= 2 ? 2 : (unroll == 4 ? 4 : 8);
+  const int u = unroll <= 2 ? 2 : (unroll == 4 ? 4 : (unroll == 6 ? 6 : 8));
   const int own = u * pipe_depth(u), i64 = 4 * pipe_depth(4);
   return own > i64 ? own : i64;
 }

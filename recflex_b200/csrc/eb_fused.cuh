@@ -52,6 +52,7 @@ namespace ebk {
     case 1:                                                                                            \
     case 2: tile_stream<T, V, 2, I64, pipe_depth(2), FS>(a, ctx, b0, b1, lane, items, ring); break;       \
     case 4: tile_stream<T, V, 4, I64, pipe_depth(4), FS>(a, ctx, b0, b1, lane, items, ring); break;       \
+    case 6: tile_stream<T, V, 6, I64, pipe_depth(6), FS>(a, ctx, b0, b1, lane, items, ring); break;       \
     default: tile_stream<T, V, 8, I64, pipe_depth(8), FS>(a, ctx, b0, b1, lane, items, ring); break;      \
   }
 

@@ -16,7 +16,7 @@ namespace ebk {
 
 FusedKernel EB_CAT(fused_kernel_occ, EB_OCC)(bool timing, int kind, int unroll) {
   if (timing) return static_cast<FusedKernel>(eb_fused_kernel<EB_OCC, true>);
-  EB_FLAVOR(5, 0) EB_FLAVOR(5, 2) EB_FLAVOR(5, 4) EB_FLAVOR(5, 8)
+  EB_FLAVOR(5, 0) EB_FLAVOR(5, 2) EB_FLAVOR(5, 4) EB_FLAVOR(5, 6) EB_FLAVOR(5, 8)
   EB_FLAVOR(4, 0) EB_FLAVOR(4, 2) EB_FLAVOR(4, 4) EB_FLAVOR(4, 8)
   return static_cast<FusedKernel>(eb_fused_kernel<EB_OCC, false>);
 }

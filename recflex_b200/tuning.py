@@ -38,7 +38,7 @@ from . import _lib
 from .rec_modules import FeatEmbed, Schedule
 
 KINDS = ("group", "warp", "flat", "stream", "pipe")
-UNROLLS = (1, 2, 4, 8)
+UNROLLS = (1, 2, 4, 6, 8)
 
 
 @dataclass
@@ -54,7 +54,7 @@ class TuneConfig:
     cluster: bool = True          # tune one representative per cluster of look-alike features
     max_probe_bytes: int = 2 << 30  # cap of the local stage's output buffer
     uniform_portfolio: Sequence[Tuple[str, int]] = (("stream", 2), ("stream", 4), ("stream", 8), ("warp", 4),
-                                                    ("pipe", 2), ("pipe", 4), ("pipe", 8))
+                                                    ("pipe", 2), ("pipe", 4), ("pipe", 6), ("pipe", 8))
     hybrid_min_len: Sequence[int] = (32, 128)  # warp-per-bag kernel for features whose mean bag is at least this long
     overlaps: Sequence[int] = (1, 2, 3)  # fused-kernel CTAs per SM tried with the warp-per-bag kernel beside it
     refine_top: int = 3           # local-stage candidates tried per cluster in the refinement pass (0 = off)
@@ -183,6 +183,8 @@ class Tuner:
                     continue  # one-hot: a bag never has a second row to keep in flight
                 if kind == "pipe" and u == 1:
                     continue  # the ring's shallowest variant is unroll 2
+                if u == 6 and kind != "pipe":
+                    continue  # six rows per macro-step exist for the ring only (48 KB of it: 4 CTAs per SM)
                 if kind == "warp" and u not in (2, 4):
                     continue  # the warp-per-bag kernel keeps two or four rows per lane in flight
                 cands.append(Schedule(kind, u))

@@ -30,6 +30,27 @@ def test_cfg1_every_schedule(cfg1, kind, unroll):
     check_against_oracle(out, tables, values, offsets, "f32")
 
 
+@pytest.mark.parametrize("cfg_id,scale,batch,tag", [(3, 2e-4, 700, "f16"), (2, 0.01, 515, "f32"), (5, 0.01, 300, "f32")])
+def test_pipe_with_six_rows_per_macro_step(cfg_id, scale, batch, tag):
+    """The 48 KB ring of the pipelined schedule (unroll 6, two macro-steps deep): the one unroll that is not a power
+    of two; and only the pipelined schedule takes it."""
+    from recflex_b200._lib import EbError
+
+    cfg, tables, values, offsets = small_model(cfg_id, scale, batch)
+    mod = FeatEmbed("cuda:0", embed_tables=device_tables(tables))
+    dv, do = to_device(values), to_device(offsets)
+    for occ in (3, 4):
+        mod.set_schedules(all_schedules("pipe", 6, len(tables)), occupancy=occ)
+        out = mod(dv, do)
+        mod.check_status()
+        check_against_oracle(out, tables, values, offsets, tag)
+    mixed = [Schedule("pipe", 6) if f % 2 else Schedule("stream", 4) for f in range(len(tables))]
+    mod.set_schedules(mixed, occupancy=4)  # the kernel with every schedule
+    check_against_oracle(mod(dv, do), tables, values, offsets, tag)
+    with pytest.raises(EbError):
+        mod.set_schedules(all_schedules("stream", 6, len(tables)))
+
+
 @pytest.mark.parametrize("occupancy", [1, 2, 3, 4, 5, 6, 7, 8])
 def test_cfg1_every_occupancy(cfg1, occupancy):
     cfg, tables, values, offsets, mod = cfg1

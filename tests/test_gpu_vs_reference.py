@@ -21,6 +21,9 @@ REF_LIB = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__)
 @pytest.fixture(scope="module")
 def ref():
     if not os.path.exists(REF_LIB):
+        if os.environ.get("RECFLEX_REF"):
+            pytest.fail("a RecFlex checkout is configured ($RECFLEX_REF) but oracle/_ref/libref_kernels.so was not "
+                        "built: run oracle/build_ref.sh")
         pytest.skip("oracle/_ref/libref_kernels.so was not built (needs the reference checkout: oracle/build_ref.sh)")
     lib = C.CDLL(REF_LIB)
     lib.ref_pool_feature.restype = C.c_int

@@ -38,5 +38,5 @@ def test_committed_schedule_files_fit_their_workloads():
         assert len(res.schedules) == len(synth.make_config(cfg_id, row_scale=1e-4).features)
         assert 1 <= res.occupancy <= 8 and 0 <= res.overlap <= res.occupancy
         for s in res.schedules:
-            assert s.kind in _lib.SCHED_NAMES and s.unroll in (1, 2, 4, 8)
+            assert s.kind in _lib.SCHED_NAMES and s.unroll in (1, 2, 4, 6, 8)
             assert s.bags_per_tile == 0 or (s.bags_per_tile & (s.bags_per_tile - 1)) == 0
