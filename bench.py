@@ -828,7 +828,8 @@ def measure_sharded(args, dev, world, rank, exchanges, row_scale, steps, tune, n
             odt = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[out_dtype]
         chunks = args.chunks or (8 if exchange == "copy" else 4)
         mod = ShardedFeatEmbed(rank, world, owner, dims, local_tables=tables, device=dev, chunks=chunks,
-                               exchange=exchange, out_dtype=odt if exchange != "nccl" else torch.float32)
+                               exchange=exchange, out_dtype=odt if exchange != "nccl" else torch.float32,
+                               columns="blocks" if exchange == "copy" else "owner")
         mod.set_batch_for_empty_rank(B)
         if mod.local is not None:
             mod.local.set_schedules(scheds, occupancy=occ)
@@ -836,6 +837,8 @@ def measure_sharded(args, dev, world, rank, exchanges, row_scale, steps, tune, n
         run_step = (lambda v, o: mod(v, o, out=out_buf)) if exchange == "nccl" else (lambda v, o: mod(v, o))
         rec = {"chunks": chunks if exchange != "peer" else 1,
                "row_dtype": "f32" if (exchange == "nccl" or odt == torch.float32) else ("bf16" if odt == torch.bfloat16 else "f16")}
+        if exchange == "copy":
+            rec["result_layout"] = "one [B / N, sum(dims of rank s)] block per owner rank"
         sent = max(summ["exchange_per_rank"]) * (1.0 if rec["row_dtype"] == "f32" else 0.5)
         rec["bytes_sent_per_rank_per_step"] = int(sent)
         try:
@@ -873,7 +876,8 @@ def measure_sharded(args, dev, world, rank, exchanges, row_scale, steps, tune, n
                     hv, ho = host[i % nb]
                     dv = [x.to(dev, non_blocking=True) for x in hv]
                     do = [x.to(dev, non_blocking=True) for x in ho]
-                    host_out.copy_(run_step(dv, do), non_blocking=True)
+                    res_i = run_step(dv, do)
+                    host_out.copy_(torch.cat(res_i, dim=1) if isinstance(res_i, list) else res_i, non_blocking=True)
 
                 t4 = timed(e2e_step, steps)
                 stats = torch.tensor([t4], dtype=torch.float64, device=dev)
@@ -903,7 +907,7 @@ def default_exchanges(args, world):
                 raise SystemExit(f"unknown exchange {x!r}")
         return names
     # fp32 rows are the contract; the bf16 entry shows what a consumer that casts anyway (RecomModel in bf16) gets
-    return ["peer", "copy", "peer:bf16"] if world >= 8 else ["peer", "peer:bf16"]
+    return ["peer", "copy", "peer:bf16"] if world >= 4 else ["peer", "peer:bf16"]
 
 
 def run_sharded(args):

@@ -582,8 +582,11 @@ int eb_forward_exchange(eb_handle* h, int64_t batch, const void* const* values_p
       cudaStream_t cst = static_cast<cudaStream_t>(copy_streams[(i - 1) % ns]);
       const char* src = reinterpret_cast<const char*>(send) + ((size_t)d * a.dest_rows + (size_t)k * a.chunk_rows) * send_ld * es;
       char* dst = reinterpret_cast<char*>(peer_out[d]) + ((size_t)k * a.chunk_rows * out_ld + out_col) * es;
-      EB_CUDA(cudaMemcpy2DAsync(dst, (size_t)out_ld * es, src, (size_t)send_ld * es, width, (size_t)a.chunk_rows,
-                                cudaMemcpyDefault, cst));
+      if ((size_t)out_ld * es == width && (size_t)send_ld * es == width)  // rows back to back on both sides: one run
+        EB_CUDA(cudaMemcpyAsync(dst, src, width * (size_t)a.chunk_rows, cudaMemcpyDefault, cst));
+      else
+        EB_CUDA(cudaMemcpy2DAsync(dst, (size_t)out_ld * es, src, (size_t)send_ld * es, width, (size_t)a.chunk_rows,
+                                  cudaMemcpyDefault, cst));
     }
   }
   return EB_OK;

@@ -20,8 +20,9 @@ every rank that all kernels are done.  It hides the transfer completely at 2 and
 the copy engines do: the kernel pools into a local send buffer in ONE launch whose tile order walks the batch piece
 by piece, and a copy stream ships every finished piece as one 2-D copy per destination (rows of sum(local dims)
 elements) while the next piece is pooled (`eb_forward_exchange`).  Its result has the columns grouped by owner rank
-(`column_of[f]` says where feature f starts); `columns="canonical"` adds a placement pass that restores feature
-order.  `exchange="nccl"` is the library baseline: pool into a send buffer, `all_to_all_single`, placement kernel.
+(`column_of[f]` says where feature f starts); `columns="blocks"` returns one `[B / world, sum(dims of rank s)]`
+tensor per owner rank instead (every copy is then one contiguous run on both sides), and `columns="canonical"` adds a
+placement pass that restores feature order.  `exchange="nccl"` is the library baseline: pool into a send buffer, `all_to_all_single`, placement kernel.
 
 With `exchange="nccl"`, batch chunks pipeline the exchange behind the pooling: chunk k's all-to-all runs on a side stream
 while chunk k + 1 is pooled.  With C chunks, sample b of the batch belongs to chunk `b // (B / C)` and,
@@ -242,8 +243,10 @@ class ShardedFeatEmbed:
             raise ValueError("the peer and copy exchanges exist only on GPUs")
         if out_dtype != torch.float32 and exchange == "nccl":
             raise ValueError("the NCCL exchange carries fp32 rows only")
-        if columns not in ("owner", "canonical"):
-            raise ValueError("columns must be 'owner' or 'canonical'")
+        if columns not in ("owner", "canonical", "blocks"):
+            raise ValueError("columns must be 'owner', 'canonical' or 'blocks'")
+        if columns == "blocks" and exchange != "copy":
+            raise ValueError("per-owner blocks are a result layout of the copy exchange")
         if columns == "canonical" and out_dtype != torch.float32:
             raise ValueError("the placement pass restores feature order for fp32 rows only")
         self.exchange, self.out_dtype, self.columns = exchange, out_dtype, columns
@@ -257,7 +260,7 @@ class ShardedFeatEmbed:
             self.owner_major_col.append(nxt[o])
             nxt[o] += self.dims[f]
         # where feature f starts in a row of the result
-        self.column_of = self.owner_major_col if (exchange == "copy" and columns == "owner") else self.col_of
+        self.column_of = self.owner_major_col if (exchange == "copy" and columns != "canonical") else self.col_of
         self._copy_done = [None, None]
         self._peer = None    # (batch, own pointers, per-buffer pointer lists, output views, mapped peer pointers)
         self._step = 0
@@ -425,9 +428,19 @@ class ShardedFeatEmbed:
         cur = torch.cuda.current_stream(self.device)
         if self._copy_done[b] is not None:
             cur.wait_event(self._copy_done[b])  # the copies that read this send buffer two calls ago are done
+        rows = batch // W
+        es = 4 if self.out_dtype == torch.float32 else 2
+        blocked = self.columns != "owner"
         if self.local is not None:
-            self.local.forward_exchange(values, offsets, self._send[b], ptrs[b], self.rank, self.units,
-                                        self.block_col[self.rank], Cn, self._copy_streams)
+            if blocked:
+                # the result buffer holds one contiguous block [rows, units of rank s] per owner rank s: every copy is
+                # one contiguous run on both sides
+                mine = rows * self.block_col[self.rank] * es
+                self.local.forward_exchange(values, offsets, self._send[b], [p + mine for p in ptrs[b]], self.rank,
+                                            self.local_units, 0, Cn, self._copy_streams)
+            else:
+                self.local.forward_exchange(values, offsets, self._send[b], ptrs[b], self.rank, self.units,
+                                            self.block_col[self.rank], Cn, self._copy_streams)
         with torch.cuda.stream(self._comm):
             self._comm.wait_stream(cur)  # the kernel stores this rank's own samples itself
             for cs in self._copy_streams:
@@ -439,22 +452,13 @@ class ShardedFeatEmbed:
         cur.wait_stream(self._comm)
         if self.columns == "owner":
             return views[b]
-        rows = batch // W
+        flat = views[b].view(-1)
+        if self.columns == "blocks":
+            return [flat[rows * self.block_col[s2]: rows * (self.block_col[s2] + self.units_of[s2])].view(rows, self.units_of[s2])
+                    for s2 in range(W)]
         if out is None:
             out = torch.empty((rows, self.units), dtype=torch.float32, device=self.device)
-        key = ("copy", rows)
-        segs = self._segs.get(key)
-        if segs is None:
-            import numpy as np
-
-            rec = np.zeros(len(self.dims), dtype=[("src_off", "<i8"), ("src_ld", "<i4"), ("dst_col", "<i4"),
-                                                  ("width", "<i4"), ("pad", "<i4")])
-            for f in range(len(self.dims)):
-                rec[f] = (self.owner_major_col[f], self.units, self.col_of[f], self.dims[f], 0)
-            segs = self._segs[key] = torch.from_numpy(rec.view(np.uint8).copy()).to(self.device)
-        _lib.check(self._lib.eb_place_columns(C.c_void_p(views[b].data_ptr()), C.c_void_p(out.data_ptr()), rows,
-                                              out.stride(0), len(self.dims), C.c_void_p(segs.data_ptr()),
-                                              self.device.index, C.c_void_p(cur.cuda_stream)))
+        self._place(flat, out, rows)  # blocks -> feature order
         return out
 
     def _forward_peer(self, values, offsets, batch: int) -> torch.Tensor:

@@ -31,7 +31,7 @@ def test_sharded_forward_fused_peer_exchange():
     _run(world, ["--exchange", "peer", "--batch", str(world * 1024)])
 
 
-@pytest.mark.parametrize("columns", ["owner", "canonical"])
+@pytest.mark.parametrize("columns", ["owner", "canonical", "blocks"])
 def test_sharded_forward_copy_engine_exchange(columns):
     world = _world()
     _run(world, ["--exchange", "copy", "--chunks", "4", "--batch", str(world * 1024), "--columns", columns])
