@@ -826,10 +826,10 @@ def measure_sharded(args, dev, world, rank, exchanges, row_scale, steps, tune, n
             odt = {"bf16": torch.bfloat16, "f16": torch.float16}[entry.split(":")[1]]
         else:
             odt = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[out_dtype]
-        chunks = args.chunks or (8 if exchange == "copy" else 4)
+        chunks = args.chunks or (8 if exchange in ("copy", "push") else 4)
         mod = ShardedFeatEmbed(rank, world, owner, dims, local_tables=tables, device=dev, chunks=chunks,
                                exchange=exchange, out_dtype=odt if exchange != "nccl" else torch.float32,
-                               columns="blocks" if exchange == "copy" else "owner")
+                               columns="blocks" if exchange in ("copy", "push") else "owner")
         mod.set_batch_for_empty_rank(B)
         if mod.local is not None:
             mod.local.set_schedules(scheds, occupancy=occ)
@@ -837,7 +837,7 @@ def measure_sharded(args, dev, world, rank, exchanges, row_scale, steps, tune, n
         run_step = (lambda v, o: mod(v, o, out=out_buf)) if exchange == "nccl" else (lambda v, o: mod(v, o))
         rec = {"chunks": chunks if exchange != "peer" else 1,
                "row_dtype": "f32" if (exchange == "nccl" or odt == torch.float32) else ("bf16" if odt == torch.bfloat16 else "f16")}
-        if exchange == "copy":
+        if exchange in ("copy", "push"):
             rec["result_layout"] = "one [B / N, sum(dims of rank s)] block per owner rank"
         sent = max(summ["exchange_per_rank"]) * (1.0 if rec["row_dtype"] == "f32" else 0.5)
         rec["bytes_sent_per_rank_per_step"] = int(sent)
@@ -903,7 +903,8 @@ def default_exchanges(args, world):
     if args.exchange:
         names = [x for x in args.exchange.split(",") if x]
         for x in names:
-            if x.split(":")[0] not in ("peer", "copy", "nccl") or x.split(":")[-1] not in ("peer", "copy", "nccl", "bf16", "f16"):
+            if x.split(":")[0] not in ("peer", "copy", "push", "nccl") or \
+                    x.split(":")[-1] not in ("peer", "copy", "push", "nccl", "bf16", "f16"):
                 raise SystemExit(f"unknown exchange {x!r}")
         return names
     # fp32 rows are the contract; the bf16 entry shows what a consumer that casts anyway (RecomModel in bf16) gets

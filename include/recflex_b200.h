@@ -348,6 +348,20 @@ int eb_forward_exchange(eb_handle* h, int64_t batch, const void* const* values_p
                         void* const* copy_streams, int num_copy_streams);
 
 /*
+ * Who ships the finished pieces of eb_forward_exchange (no counterpart in the
+ * reference).  EB_EXCHANGE_COPY_ENGINES (default): cudaMemcpy2DAsync /
+ * cudaMemcpyAsync on the copy streams.  EB_EXCHANGE_SM_PUSH: a small kernel on
+ * the first copy stream (128-thread CTAs that fit beside the pooling kernel's),
+ * whose warps load 512-byte runs of the send buffer and store them to the peer,
+ * so that full lines cross NVLink; needs rows, leading dimensions and column
+ * offsets that are multiples of 16 bytes and falls back to the copy engines
+ * otherwise.
+ */
+#define EB_EXCHANGE_COPY_ENGINES 0
+#define EB_EXCHANGE_SM_PUSH 1
+int eb_set_exchange_engine(eb_handle* h, int engine);
+
+/*
  * Overlap of the two pooling kernels (no counterpart in the reference, whose
  * single generated kernel holds every schedule).  0 (the default): features on
  * EB_SCHED_WARP are pooled by their own kernel, then the fused kernel pools the

@@ -22,6 +22,7 @@ EB_ERR_TOO_LARGE = -6
 EB_F32, EB_F16 = 0, 1
 EB_I32, EB_I64 = 0, 1
 EB_OUT_F32, EB_OUT_BF16, EB_OUT_F16 = 0, 1, 2
+EB_EXCHANGE_COPY_ENGINES, EB_EXCHANGE_SM_PUSH = 0, 1
 EB_NOALLOC_MAX_FEATURES = 1024
 EB_SCHED_AUTO, EB_SCHED_GROUP, EB_SCHED_WARP, EB_SCHED_FLAT, EB_SCHED_STREAM, EB_SCHED_PIPE = 0, 1, 2, 3, 4, 5
 SCHED_NAMES = {EB_SCHED_AUTO: "auto", EB_SCHED_GROUP: "group", EB_SCHED_WARP: "warp", EB_SCHED_FLAT: "flat",
@@ -95,6 +96,7 @@ PROTOTYPES = {
     "eb_noalloc_check_status": (C.c_int, [C.c_int, C.c_void_p]),
     "eb_set_output_dtype": (C.c_int, [C.c_void_p, C.c_int]),
     "eb_set_long_bag_split": (C.c_int, [C.c_void_p, C.c_int64]),
+    "eb_set_exchange_engine": (C.c_int, [C.c_void_p, C.c_int]),
     "eb_forward_exchange": (C.c_int, [C.c_void_p, C.c_int64, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
                                       C.POINTER(C.c_int64), C.c_int, C.c_int, C.c_void_p, C.c_int64,
                                       C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int,

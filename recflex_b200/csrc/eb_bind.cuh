@@ -191,6 +191,52 @@ __global__ void eb_release_kernel(uint32_t* flags, int n, uint32_t epoch) {
 }
 
 // ---------------------------------------------------------------------------
+// eb_push_kernel: ships one finished piece of the send buffer to the other ranks with the SMs instead of the copy
+// engines.  Small CTAs (128 threads, few registers) that fit beside the persistent pooling CTAs; every warp moves
+// whole 512-byte runs (32 lanes x 16 bytes, loaded from local memory, stored to the peer), so what crosses NVLink is
+// full lines, unlike the 64 to 512-byte pieces the pooling kernel itself would store.  Needs rows, leading dimensions
+// and column offsets that are multiples of 16 bytes.
+// ---------------------------------------------------------------------------
+struct PushArgs {
+  const char* send;        // first row of destination 0's piece is send + (0 * dest_rows + piece * piece_rows) * send_ld_b
+  char* peer[kMaxPeers];   // result matrices (already advanced to this rank's column block)
+  long long send_ld_b, out_ld_b;
+  long long dest_rows, piece_rows, piece;
+  int width16;             // 16-byte units per row
+  int world, rank;
+};
+
+__global__ void __launch_bounds__(128) eb_push_kernel(PushArgs p) {
+  const long long per_dest = p.piece_rows * p.width16;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (int i = 1; i < p.world; ++i) {
+    const int d = (p.rank + i) % p.world;
+    const char* src0 = p.send + (d * p.dest_rows + p.piece * p.piece_rows) * p.send_ld_b;
+    char* dst0 = p.peer[d] + p.piece * p.piece_rows * p.out_ld_b;
+    long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; u + 3 * stride < per_dest; u += 4 * stride) {  // four loads in flight per thread, then four stores
+      uint4 v[4];
+      long long row[4];
+      int c[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const long long uu = u + k * stride;
+        row[k] = uu / p.width16;
+        c[k] = (int)(uu - row[k] * p.width16);
+        v[k] = __ldcs(reinterpret_cast<const uint4*>(src0 + row[k] * p.send_ld_b) + c[k]);
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) *(reinterpret_cast<uint4*>(dst0 + row[k] * p.out_ld_b) + c[k]) = v[k];
+    }
+    for (; u < per_dest; u += stride) {
+      const long long row = u / p.width16;
+      const int c = (int)(u - row * p.width16);
+      *(reinterpret_cast<uint4*>(dst0 + row * p.out_ld_b) + c) = __ldcs(reinterpret_cast<const uint4*>(src0 + row * p.send_ld_b) + c);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // table fill: counter-based synthetic weights (bit-reproducible on the CPU)
 // ---------------------------------------------------------------------------
 __host__ __device__ inline uint64_t mix64(uint64_t x) {

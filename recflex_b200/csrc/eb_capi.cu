@@ -96,6 +96,7 @@ struct eb_handle {
   int out_dtype = EB_OUT_F32;  // element type of the output matrix
   int only_kind = 0, only_unroll = 0;   // the one schedule (and unroll) every fused-kernel feature uses, 0 = mixed
   int64_t long_bag_bytes = 1 << 20;     // bags gathering at least this much are pooled by eb_longbag_kernel (0 = off)
+  int exchange_engine = EB_EXCHANGE_COPY_ENGINES;  // who ships the pieces of eb_forward_exchange
   uint32_t epoch = 0;          // calls in chunked ticket order so far (eb_forward_exchange)
 };
 
@@ -501,6 +502,14 @@ int eb_set_long_bag_split(eb_handle* h, int64_t min_bytes) {
   return EB_OK;
 }
 
+int eb_set_exchange_engine(eb_handle* h, int engine) {
+  if (!h) return fail(EB_ERR_INVALID_ARG, "null handle");
+  if (engine != EB_EXCHANGE_COPY_ENGINES && engine != EB_EXCHANGE_SM_PUSH)
+    return fail(EB_ERR_INVALID_ARG, "engine must be EB_EXCHANGE_COPY_ENGINES or EB_EXCHANGE_SM_PUSH (got %d)", engine);
+  h->exchange_engine = engine;
+  return EB_OK;
+}
+
 int eb_set_output_dtype(eb_handle* h, int out_dtype) {
   if (!h) return fail(EB_ERR_INVALID_ARG, "null handle");
   if (out_dtype != EB_OUT_F32 && out_dtype != EB_OUT_BF16 && out_dtype != EB_OUT_F16)
@@ -571,6 +580,26 @@ int eb_forward_exchange(eb_handle* h, int64_t batch, const void* const* values_p
   const ChunkSync* cs = reinterpret_cast<const ChunkSync*>(static_cast<char*>(workspace) + ws_layout(h->num_features).chunk_sync);
   const size_t width = (size_t)h->units * es;
   const int ns = num_copy_streams < world - 1 ? num_copy_streams : (world > 1 ? world - 1 : 1);
+  // SM copies need 16-byte granularity everywhere; otherwise the copy engines do the work
+  const bool push = h->exchange_engine == EB_EXCHANGE_SM_PUSH && width % 16 == 0 && ((size_t)send_ld * es) % 16 == 0 &&
+                    ((size_t)out_ld * es) % 16 == 0 && ((size_t)out_col * es) % 16 == 0 &&
+                    (reinterpret_cast<uintptr_t>(send) & 15) == 0;
+  void* blocks[kMaxPeers] = {};
+  bool aligned = push;
+  for (int r = 0; r < world; ++r) {
+    blocks[r] = reinterpret_cast<char*>(peer_out[r]) + (size_t)out_col * es;
+    aligned = aligned && (reinterpret_cast<uintptr_t>(blocks[r]) & 15) == 0;
+  }
+  if (aligned && world > 1) {
+    cudaStream_t cst = static_cast<cudaStream_t>(copy_streams[0]);
+    for (int k = 0; k < chunks; ++k) {
+      const int wrc = wait32(cst, (unsigned long long)reinterpret_cast<uintptr_t>(&cs->flag[k]), a.epoch, 0u /* >= */);
+      if (wrc != 0) return fail(EB_ERR_CUDA, "cuStreamWaitValue32 failed with driver error %d", wrc);
+      EB_CUDA(launch_push(send, blocks, (long long)send_ld * es, (long long)out_ld * es, a.dest_rows, a.chunk_rows, k,
+                          (int)(width / 16), world, rank, h->sm_count, cst));
+    }
+    return EB_OK;
+  }
   for (int k = 0; k < chunks; ++k) {
     for (int j = 0; j < ns && world > 1; ++j) {
       const int wrc = wait32(static_cast<cudaStream_t>(copy_streams[j]),

@@ -61,6 +61,24 @@ static int helper_grid(int64_t wanted, int ctas_per_sm) {
   return (int)(wanted < 1 ? 1 : (wanted > cap ? cap : wanted));
 }
 
+cudaError_t launch_push(const void* send, void* const* peer, long long send_ld_b, long long out_ld_b, long long dest_rows,
+                        long long piece_rows, long long piece, int width16, int world, int rank, int sm_count,
+                        cudaStream_t st) {
+  PushArgs p;
+  p.send = static_cast<const char*>(send);
+  for (int r = 0; r < kMaxPeers; ++r) p.peer[r] = r < world ? static_cast<char*>(peer[r]) : nullptr;
+  p.send_ld_b = send_ld_b;
+  p.out_ld_b = out_ld_b;
+  p.dest_rows = dest_rows;
+  p.piece_rows = piece_rows;
+  p.piece = piece;
+  p.width16 = width16;
+  p.world = world;
+  p.rank = rank;
+  eb_push_kernel<<<sm_count, 128, 0, st>>>(p);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_fused(const LaunchArgs& a, int occupancy, bool timing, int grid, size_t smem_bytes, cudaStream_t st,
                          int kind, int unroll) {
   if (a.idx64 || timing) kind = unroll = 0;  // the specialised instantiations read 32-bit indices and keep no clocks

@@ -163,6 +163,12 @@ class FeatEmbed(nn.Module):
         instead of by the one warp that meets them; 0 pools every bag in place."""
         _lib.check(self._lib.eb_set_long_bag_split(self._h, int(min_bytes)))
 
+    def set_exchange_engine(self, engine: str) -> None:
+        """Who ships the finished pieces of `forward_exchange`: 'copy' (the copy engines, default) or 'push' (a small
+        kernel whose warps store 512-byte runs to the peers)."""
+        code = {"copy": _lib.EB_EXCHANGE_COPY_ENGINES, "push": _lib.EB_EXCHANGE_SM_PUSH}[engine]
+        _lib.check(self._lib.eb_set_exchange_engine(self._h, code))
+
     def _check_out(self, out: Optional[torch.Tensor], batch: int) -> torch.Tensor:
         if out is None:
             return torch.empty((batch, self.output_units), dtype=self.output_dtype, device=self.device)

@@ -22,7 +22,8 @@ by piece, and a copy stream ships every finished piece as one 2-D copy per desti
 elements) while the next piece is pooled (`eb_forward_exchange`).  Its result has the columns grouped by owner rank
 (`column_of[f]` says where feature f starts); `columns="blocks"` returns one `[B / world, sum(dims of rank s)]`
 tensor per owner rank instead (every copy is then one contiguous run on both sides), and `columns="canonical"` adds a
-placement pass that restores feature order.  `exchange="nccl"` is the library baseline: pool into a send buffer, `all_to_all_single`, placement kernel.
+placement pass that restores feature order.  `exchange="push"` is the copy exchange with the pieces shipped by a small kernel (warps storing 512-byte runs to
+the peers) instead of the copy engines.  `exchange="nccl"` is the library baseline: pool into a send buffer, `all_to_all_single`, placement kernel.
 
 With `exchange="nccl"`, batch chunks pipeline the exchange behind the pooling: chunk k's all-to-all runs on a side stream
 while chunk k + 1 is pooled.  With C chunks, sample b of the batch belongs to chunk `b // (B / C)` and,
@@ -237,15 +238,15 @@ class ShardedFeatEmbed:
             self.device = torch.device(device) if device is not None else torch.device("cpu")
         self._segs = {}      # rows per chunk -> device descriptor tensor for the placement kernel
         self._bufs = {}
-        if exchange not in ("nccl", "peer", "copy"):
-            raise ValueError("exchange must be 'nccl', 'peer' or 'copy'")
+        if exchange not in ("nccl", "peer", "copy", "push"):
+            raise ValueError("exchange must be 'nccl', 'peer', 'copy' or 'push'")
         if exchange != "nccl" and pool_fn is not None:
             raise ValueError("the peer and copy exchanges exist only on GPUs")
         if out_dtype != torch.float32 and exchange == "nccl":
             raise ValueError("the NCCL exchange carries fp32 rows only")
         if columns not in ("owner", "canonical", "blocks"):
             raise ValueError("columns must be 'owner', 'canonical' or 'blocks'")
-        if columns == "blocks" and exchange != "copy":
+        if columns == "blocks" and exchange not in ("copy", "push"):
             raise ValueError("per-owner blocks are a result layout of the copy exchange")
         if columns == "canonical" and out_dtype != torch.float32:
             raise ValueError("the placement pass restores feature order for fp32 rows only")
@@ -260,7 +261,9 @@ class ShardedFeatEmbed:
             self.owner_major_col.append(nxt[o])
             nxt[o] += self.dims[f]
         # where feature f starts in a row of the result
-        self.column_of = self.owner_major_col if (exchange == "copy" and columns != "canonical") else self.col_of
+        self.column_of = self.owner_major_col if (exchange in ("copy", "push") and columns != "canonical") else self.col_of
+        if exchange == "push" and self.local is not None:
+            self.local.set_exchange_engine("push")  # the copy exchange with SM copies instead of the copy engines
         self._copy_done = [None, None]
         self._peer = None    # (batch, own pointers, per-buffer pointer lists, output views, mapped peer pointers)
         self._step = 0
@@ -307,7 +310,7 @@ class ShardedFeatEmbed:
             batch = self._empty_rank_batch
         if self.exchange == "peer":
             return self._forward_peer(values, offsets, batch)
-        if self.exchange == "copy":
+        if self.exchange in ("copy", "push"):
             return self._forward_copy(values, offsets, batch, out)
         if batch % (W * Cn) != 0:
             raise ValueError(f"batch {batch} must be a multiple of world * chunks = {W * Cn}")

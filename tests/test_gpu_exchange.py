@@ -36,7 +36,8 @@ def _rank_module(cfg, tables, owner, rank, kind):
 
 @pytest.mark.parametrize("kind", ["stream", "pipe", "warp"])
 @pytest.mark.parametrize("chunks", [1, 8])
-def test_copy_engine_exchange_on_one_device(kind, chunks):
+@pytest.mark.parametrize("engine", ["copy", "push"])
+def test_copy_engine_exchange_on_one_device(kind, chunks, engine):
     world, rows = 4, 256
     cfg, tables, values, offsets, owner = _cfg4_scaled(world, rows)
     B, units = cfg.batch, cfg.output_units
@@ -46,6 +47,7 @@ def test_copy_engine_exchange_on_one_device(kind, chunks):
     column_of, block = [0] * len(cfg.features), 0
     for rank in range(world):
         local, mod = _rank_module(cfg, tables, owner, rank, kind)
+        mod.set_exchange_engine(engine)  # who ships the pieces: the copy engines, or a small kernel
         send = torch.full((B, mod.output_units), float("nan"), device="cuda:0")
         dv = [torch.from_numpy(values[f]).cuda() for f in local]
         do = [torch.from_numpy(offsets[f]).cuda() for f in local]

@@ -37,7 +37,7 @@ def test_sharded_forward_copy_engine_exchange(columns):
     _run(world, ["--exchange", "copy", "--chunks", "4", "--batch", str(world * 1024), "--columns", columns])
 
 
-@pytest.mark.parametrize("exchange,chunks", [("peer", 1), ("copy", 8), ("nccl", 4)])
+@pytest.mark.parametrize("exchange,chunks", [("peer", 1), ("copy", 8), ("push", 8), ("nccl", 4)])
 def test_sharded_cfg4_shaped_plan(exchange, chunks):
     """The sharded benchmark configuration scaled down: 400 features, the benchmark's planner call, every exchange."""
     world = _world()
