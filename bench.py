@@ -822,6 +822,9 @@ def measure_sharded(args, dev, world, rank, exchanges, row_scale, steps, tune, n
 
     for entry in exchanges:
         exchange = entry.split(":")[0]
+        direct_hops = 0
+        if exchange.startswith("hybrid"):  # hybridK: copy exchange with the K nearest destinations served by stores
+            direct_hops, exchange = int(exchange[6:] or world // 2), "copy"
         if ":" in entry:
             odt = {"bf16": torch.bfloat16, "f16": torch.float16}[entry.split(":")[1]]
         else:
@@ -829,13 +832,13 @@ def measure_sharded(args, dev, world, rank, exchanges, row_scale, steps, tune, n
         chunks = args.chunks or (8 if exchange in ("copy", "push") else 4)
         mod = ShardedFeatEmbed(rank, world, owner, dims, local_tables=tables, device=dev, chunks=chunks,
                                exchange=exchange, out_dtype=odt if exchange != "nccl" else torch.float32,
-                               columns="blocks" if exchange in ("copy", "push") else "owner")
+                               columns="blocks" if exchange in ("copy", "push") else "owner", direct_hops=direct_hops)
         mod.set_batch_for_empty_rank(B)
         if mod.local is not None:
             mod.local.set_schedules(scheds, occupancy=occ)
         out_buf = torch.empty((B // world, cfg.output_units), dtype=torch.float32, device=dev) if exchange == "nccl" else None
         run_step = (lambda v, o: mod(v, o, out=out_buf)) if exchange == "nccl" else (lambda v, o: mod(v, o))
-        rec = {"chunks": chunks if exchange != "peer" else 1,
+        rec = {"chunks": chunks if exchange != "peer" else 1, "direct_hops": direct_hops,
                "row_dtype": "f32" if (exchange == "nccl" or odt == torch.float32) else ("bf16" if odt == torch.bfloat16 else "f16")}
         if exchange in ("copy", "push"):
             rec["result_layout"] = "one [B / N, sum(dims of rank s)] block per owner rank"
@@ -903,8 +906,8 @@ def default_exchanges(args, world):
     if args.exchange:
         names = [x for x in args.exchange.split(",") if x]
         for x in names:
-            if x.split(":")[0] not in ("peer", "copy", "push", "nccl") or \
-                    x.split(":")[-1] not in ("peer", "copy", "push", "nccl", "bf16", "f16"):
+            if (x.split(":")[0] not in ("peer", "copy", "push", "nccl") and not x.startswith("hybrid")) or \
+                    (x.split(":")[-1] not in ("peer", "copy", "push", "nccl", "bf16", "f16") and ":" in x):
                 raise SystemExit(f"unknown exchange {x!r}")
         return names
     # fp32 rows are the contract; the bf16 entry shows what a consumer that casts anyway (RecomModel in bf16) gets

@@ -362,6 +362,18 @@ int eb_forward_exchange(eb_handle* h, int64_t batch, const void* const* values_p
 int eb_set_exchange_engine(eb_handle* h, int engine);
 
 /*
+ * Splits eb_forward_exchange between the two ways a row can travel (no
+ * counterpart in the reference): the rows for the `hops` ranks to the right of
+ * this one (rank + 1 ... rank + hops, modulo world) are stored by the pooling
+ * kernel straight into those ranks' result blocks, like this rank's own rows;
+ * only the remaining destinations go through the send buffer and the copy
+ * streams.  Kernel stores and copy engines are limited by different things, so
+ * together they can move more than either alone.  0 (default): every other
+ * rank is served by copies; world - 1 or more: none is.
+ */
+int eb_set_exchange_direct(eb_handle* h, int hops);
+
+/*
  * Overlap of the two pooling kernels (no counterpart in the reference, whose
  * single generated kernel holds every schedule).  0 (the default): features on
  * EB_SCHED_WARP are pooled by their own kernel, then the fused kernel pools the

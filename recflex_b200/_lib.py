@@ -97,6 +97,7 @@ PROTOTYPES = {
     "eb_set_output_dtype": (C.c_int, [C.c_void_p, C.c_int]),
     "eb_set_long_bag_split": (C.c_int, [C.c_void_p, C.c_int64]),
     "eb_set_exchange_engine": (C.c_int, [C.c_void_p, C.c_int]),
+    "eb_set_exchange_direct": (C.c_int, [C.c_void_p, C.c_int]),
     "eb_forward_exchange": (C.c_int, [C.c_void_p, C.c_int64, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
                                       C.POINTER(C.c_int64), C.c_int, C.c_int, C.c_void_p, C.c_int64,
                                       C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int,

@@ -204,12 +204,13 @@ struct PushArgs {
   long long dest_rows, piece_rows, piece;
   int width16;             // 16-byte units per row
   int world, rank;
+  int first_hop;           // destinations first_hop .. world - 1 hops to the right are served
 };
 
 __global__ void __launch_bounds__(128) eb_push_kernel(PushArgs p) {
   const long long per_dest = p.piece_rows * p.width16;
   const long long stride = (long long)gridDim.x * blockDim.x;
-  for (int i = 1; i < p.world; ++i) {
+  for (int i = p.first_hop; i < p.world; ++i) {
     const int d = (p.rank + i) % p.world;
     const char* src0 = p.send + (d * p.dest_rows + p.piece * p.piece_rows) * p.send_ld_b;
     char* dst0 = p.peer[d] + p.piece * p.piece_rows * p.out_ld_b;

@@ -97,6 +97,7 @@ struct eb_handle {
   int only_kind = 0, only_unroll = 0;   // the one schedule (and unroll) every fused-kernel feature uses, 0 = mixed
   int64_t long_bag_bytes = 1 << 20;     // bags gathering at least this much are pooled by eb_longbag_kernel (0 = off)
   int exchange_engine = EB_EXCHANGE_COPY_ENGINES;  // who ships the pieces of eb_forward_exchange
+  int exchange_direct_hops = 0;  // destinations to the right of this rank whose rows the kernel stores itself
   uint32_t epoch = 0;          // calls in chunked ticket order so far (eb_forward_exchange)
 };
 
@@ -502,6 +503,13 @@ int eb_set_long_bag_split(eb_handle* h, int64_t min_bytes) {
   return EB_OK;
 }
 
+int eb_set_exchange_direct(eb_handle* h, int hops) {
+  if (!h) return fail(EB_ERR_INVALID_ARG, "null handle");
+  if (hops < 0 || hops >= kMaxPeers) return fail(EB_ERR_INVALID_ARG, "hops must be 0..%d (got %d)", kMaxPeers - 1, hops);
+  h->exchange_direct_hops = hops;
+  return EB_OK;
+}
+
 int eb_set_exchange_engine(eb_handle* h, int engine) {
   if (!h) return fail(EB_ERR_INVALID_ARG, "null handle");
   if (engine != EB_EXCHANGE_COPY_ENGINES && engine != EB_EXCHANGE_SM_PUSH)
@@ -572,14 +580,23 @@ int eb_forward_exchange(eb_handle* h, int64_t batch, const void* const* values_p
   a.own_ld = out_ld;
   a.own_col = (int32_t)out_col;
   a.own_rank = rank;
-  a.own_vec = out_vec_of(peer_out[rank], out_ld, es);
+  a.world = world;
+  a.direct_hops = h->exchange_direct_hops < world - 1 ? h->exchange_direct_hops : world - 1;
+  a.own_vec = 2;
+  for (int r = 0; r < world; ++r) {
+    a.peer_out[r] = peer_out[r];
+    const int v = out_vec_of(peer_out[r], out_ld, es);
+    a.own_vec = v < a.own_vec ? v : a.own_vec;
+  }
+  const int first_copied = a.direct_hops + 1;  // hops first_copied .. world - 1 leave through the send buffer
   rc = run(h, a, false, st);
   if (rc != EB_OK) return rc;
   // copy streams: as soon as chunk k is published, its rows leave for every other rank; destination i hops to the
   // right of this rank uses stream (i - 1) mod n, so several copy engines work at once
   const ChunkSync* cs = reinterpret_cast<const ChunkSync*>(static_cast<char*>(workspace) + ws_layout(h->num_features).chunk_sync);
   const size_t width = (size_t)h->units * es;
-  const int ns = num_copy_streams < world - 1 ? num_copy_streams : (world > 1 ? world - 1 : 1);
+  const int copied = world - first_copied;  // destinations served by copies
+  const int ns = num_copy_streams < copied ? num_copy_streams : (copied > 0 ? copied : 1);
   // SM copies need 16-byte granularity everywhere; otherwise the copy engines do the work
   const bool push = h->exchange_engine == EB_EXCHANGE_SM_PUSH && width % 16 == 0 && ((size_t)send_ld * es) % 16 == 0 &&
                     ((size_t)out_ld * es) % 16 == 0 && ((size_t)out_col * es) % 16 == 0 &&
@@ -590,25 +607,25 @@ int eb_forward_exchange(eb_handle* h, int64_t batch, const void* const* values_p
     blocks[r] = reinterpret_cast<char*>(peer_out[r]) + (size_t)out_col * es;
     aligned = aligned && (reinterpret_cast<uintptr_t>(blocks[r]) & 15) == 0;
   }
-  if (aligned && world > 1) {
+  if (aligned && first_copied < world) {
     cudaStream_t cst = static_cast<cudaStream_t>(copy_streams[0]);
     for (int k = 0; k < chunks; ++k) {
       const int wrc = wait32(cst, (unsigned long long)reinterpret_cast<uintptr_t>(&cs->flag[k]), a.epoch, 0u /* >= */);
       if (wrc != 0) return fail(EB_ERR_CUDA, "cuStreamWaitValue32 failed with driver error %d", wrc);
       EB_CUDA(launch_push(send, blocks, (long long)send_ld * es, (long long)out_ld * es, a.dest_rows, a.chunk_rows, k,
-                          (int)(width / 16), world, rank, h->sm_count, cst));
+                          (int)(width / 16), world, rank, first_copied, h->sm_count, cst));
     }
     return EB_OK;
   }
   for (int k = 0; k < chunks; ++k) {
-    for (int j = 0; j < ns && world > 1; ++j) {
+    for (int j = 0; j < ns && first_copied < world; ++j) {
       const int wrc = wait32(static_cast<cudaStream_t>(copy_streams[j]),
                              (unsigned long long)reinterpret_cast<uintptr_t>(&cs->flag[k]), a.epoch, 0u /* >= */);
       if (wrc != 0) return fail(EB_ERR_CUDA, "cuStreamWaitValue32 failed with driver error %d", wrc);
     }
-    for (int i = 1; i < world; ++i) {
+    for (int i = first_copied; i < world; ++i) {
       const int d = (rank + i) % world;
-      cudaStream_t cst = static_cast<cudaStream_t>(copy_streams[(i - 1) % ns]);
+      cudaStream_t cst = static_cast<cudaStream_t>(copy_streams[(i - first_copied) % ns]);
       const char* src = reinterpret_cast<const char*>(send) + ((size_t)d * a.dest_rows + (size_t)k * a.chunk_rows) * send_ld * es;
       char* dst = reinterpret_cast<char*>(peer_out[d]) + ((size_t)k * a.chunk_rows * out_ld + out_col) * es;
       if ((size_t)out_ld * es == width && (size_t)send_ld * es == width)  // rows back to back on both sides: one run

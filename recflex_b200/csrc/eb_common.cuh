@@ -164,13 +164,17 @@ struct LaunchArgs {
   uint32_t epoch;         // value written to a chunk's flag when its last tile is done
   int64_t chunk_rows;
   int64_t dest_rows;
-  // chunked order: the rows of destination own_rank (this rank's own samples) skip the send buffer and go straight
-  // to own_out ([dest_rows, own_ld] elements) at columns own_col + the feature's column; null = no such shortcut
+  // chunked order: rows for this rank itself (destination own_rank) and for the direct_hops ranks to its right skip
+  // the send buffer: the kernel stores them straight into the destination's result block, peer_out[d] ([dest_rows,
+  // own_ld] elements, the same geometry on every rank) at columns own_col + the feature's column; own_out null = no
+  // such shortcut.  The other destinations' rows go to the send buffer and leave by copy.
   float* own_out;
   int64_t own_ld;
   int32_t own_col;
   int32_t own_rank;
-  int32_t own_vec;        // like out_vec, for own_out
+  int32_t own_vec;        // like out_vec, for the direct destinations' blocks
+  int32_t direct_hops;
+  int32_t world;
   int32_t pad2_;
   // peer mode (rows_per_peer > 0): sample b is stored to peer_out[b / rows_per_peer], row b % rows_per_peer
   int64_t rows_per_peer;

@@ -165,13 +165,17 @@ __global__ void __launch_bounds__(kCtaThreads, OCC) eb_fused_kernel(LaunchArgs a
     const int n = __ldg(bpt + f);
     if (a.peer_spread) tile = spread_tile(tile, n, a.peer_spread, a.rows_per_peer);
     int64_t b0 = tile * n;
-    bool own = false;  // chunked order: this tile's samples are this rank's own
+    bool own = false;  // chunked order: this tile's rows are stored straight into their destination's block
+    int64_t own_d = 0;
     if (a.chunks > 0) {
       // tile of the chunk's own bag numbering [0, world * chunk_rows): destination d's run of chunk_rows bags
       // starts at batch position d * dest_rows + chunk * chunk_rows; n divides chunk_rows
       const int64_t d = b0 / a.chunk_rows;
       b0 = d * a.dest_rows + (int64_t)chunk * a.chunk_rows + (b0 - d * a.chunk_rows);
-      own = a.own_out != nullptr && d == a.own_rank;
+      int hop = (int)d - a.own_rank;
+      hop = hop < 0 ? hop + a.world : hop;
+      own = a.own_out != nullptr && hop <= a.direct_hops;
+      own_d = d;
     }
     const int64_t b1 = (b0 + n) < a.batch ? (b0 + n) : a.batch;
 
@@ -199,8 +203,8 @@ __global__ void __launch_bounds__(kCtaThreads, OCC) eb_fused_kernel(LaunchArgs a
     ctx.has_end = a.has_end != 0;
     ctx.out_vec = (a.out_vec == 2 && (fs.col_off & 7) == 0) ? 2 : ((a.out_vec != 0 && (fs.col_off & 3) == 0) ? 1 : 0);
     if (own) {
-      // row b of the batch is row b - own_rank * dest_rows of this rank's result matrix
-      ctx.out = reinterpret_cast<char*>(a.own_out) - (((int64_t)a.own_rank * a.dest_rows * a.own_ld) << ctx.es_shift);
+      // row b of the batch is row b - d * dest_rows of destination d's block
+      ctx.out = reinterpret_cast<char*>(hdr->peer_out[own_d]) - ((own_d * a.dest_rows * a.own_ld) << ctx.es_shift);
       ctx.out_ld = a.own_ld;
       ctx.col_off = a.own_col + fs.col_off;
       ctx.out_vec = (a.own_vec == 2 && (ctx.col_off & 7) == 0) ? 2 : ((a.own_vec != 0 && (ctx.col_off & 3) == 0) ? 1 : 0);

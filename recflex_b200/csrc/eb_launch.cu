@@ -62,8 +62,8 @@ static int helper_grid(int64_t wanted, int ctas_per_sm) {
 }
 
 cudaError_t launch_push(const void* send, void* const* peer, long long send_ld_b, long long out_ld_b, long long dest_rows,
-                        long long piece_rows, long long piece, int width16, int world, int rank, int sm_count,
-                        cudaStream_t st) {
+                        long long piece_rows, long long piece, int width16, int world, int rank, int first_hop,
+                        int sm_count, cudaStream_t st) {
   PushArgs p;
   p.send = static_cast<const char*>(send);
   for (int r = 0; r < kMaxPeers; ++r) p.peer[r] = r < world ? static_cast<char*>(peer[r]) : nullptr;
@@ -75,6 +75,7 @@ cudaError_t launch_push(const void* send, void* const* peer, long long send_ld_b
   p.width16 = width16;
   p.world = world;
   p.rank = rank;
+  p.first_hop = first_hop;
   eb_push_kernel<<<sm_count, 128, 0, st>>>(p);
   return cudaGetLastError();
 }

@@ -28,8 +28,8 @@ cudaError_t launch_fused(const LaunchArgs& a, int occupancy, bool timing, int gr
                          int kind = 0, int unroll = 0);
 // Chunked order: ships piece `piece` of the send buffer to every other rank with eb_push_kernel (SM copies).
 cudaError_t launch_push(const void* send, void* const* peer, long long send_ld_b, long long out_ld_b, long long dest_rows,
-                        long long piece_rows, long long piece, int width16, int world, int rank, int sm_count,
-                        cudaStream_t st);
+                        long long piece_rows, long long piece, int width16, int world, int rank, int first_hop,
+                        int sm_count, cudaStream_t st);
 cudaError_t launch_longbag(const LaunchArgs& a, bool timing, int sm_count, cudaStream_t st);
 // eb_warp_kernel: pools the `warp_features` features on the warp-per-bag schedule (one CTA per 8 bags).
 cudaError_t launch_warp(const LaunchArgs& a, bool timing, int warp_features, cudaStream_t st);

@@ -161,11 +161,17 @@ __global__ void __launch_bounds__(kCtaThreads, kWarpKernelOccupancy) eb_warp_ker
     orow = reinterpret_cast<char*>(hdr->peer_out[d]) + (((bag - d * a.rows_per_peer) * a.out_ld + fs.col_off) << es_shift);
   }
   int out_vec = (a.out_vec == 2 && (fs.col_off & 7) == 0) ? 2 : ((a.out_vec != 0 && (fs.col_off & 3) == 0) ? 1 : 0);
-  if (a.chunks > 0 && a.own_out != nullptr && bag / a.dest_rows == a.own_rank) {
-    // chunked order: this rank's own samples go straight to its result matrix (see LaunchArgs::own_out)
-    const int col = a.own_col + fs.col_off;
-    orow = reinterpret_cast<char*>(a.own_out) + (((bag - (int64_t)a.own_rank * a.dest_rows) * a.own_ld + col) << es_shift);
-    out_vec = (a.own_vec == 2 && (col & 7) == 0) ? 2 : ((a.own_vec != 0 && (col & 3) == 0) ? 1 : 0);
+  if (a.chunks > 0 && a.own_out != nullptr) {
+    // chunked order: rows for this rank and its direct destinations go straight to the destination's block (see
+    // LaunchArgs::own_out)
+    const int64_t d = bag / a.dest_rows;
+    int hop = (int)d - a.own_rank;
+    hop = hop < 0 ? hop + a.world : hop;
+    if (hop <= a.direct_hops) {
+      const int col = a.own_col + fs.col_off;
+      orow = reinterpret_cast<char*>(hdr->peer_out[d]) + (((bag - d * a.dest_rows) * a.own_ld + col) << es_shift);
+      out_vec = (a.own_vec == 2 && (col & 7) == 0) ? 2 : ((a.own_vec != 0 && (col & 3) == 0) ? 1 : 0);
+    }
   }
   uint32_t* status = &hdr->status;
   const bool u2 = fs.unroll <= 2;  // two or four rows per lane in flight

@@ -169,6 +169,11 @@ class FeatEmbed(nn.Module):
         code = {"copy": _lib.EB_EXCHANGE_COPY_ENGINES, "push": _lib.EB_EXCHANGE_SM_PUSH}[engine]
         _lib.check(self._lib.eb_set_exchange_engine(self._h, code))
 
+    def set_exchange_direct(self, hops: int) -> None:
+        """`forward_exchange`: the rows for the `hops` ranks to the right of this one are stored by the kernel
+        straight into their result blocks; only the other destinations go through the send buffer and the copies."""
+        _lib.check(self._lib.eb_set_exchange_direct(self._h, int(hops)))
+
     def _check_out(self, out: Optional[torch.Tensor], batch: int) -> torch.Tensor:
         if out is None:
             return torch.empty((batch, self.output_units), dtype=self.output_dtype, device=self.device)

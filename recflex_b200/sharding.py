@@ -203,7 +203,7 @@ class ShardedFeatEmbed:
     def __init__(self, rank: int, world: int, owner: Sequence[int], dims: Sequence[int],
                  local_tables: Optional[List[torch.Tensor]] = None, device=None, group=None, chunks: int = 4,
                  pool_fn: Optional[Callable] = None, place_fn: Optional[Callable] = None, exchange: str = "nccl",
-                 out_dtype: torch.dtype = torch.float32, columns: str = "owner"):
+                 out_dtype: torch.dtype = torch.float32, columns: str = "owner", direct_hops: int = 0):
         if len(owner) != len(dims):
             raise ValueError("owner and dims must have one entry per feature")
         self.rank, self.world, self.group = rank, world, group
@@ -262,6 +262,9 @@ class ShardedFeatEmbed:
             nxt[o] += self.dims[f]
         # where feature f starts in a row of the result
         self.column_of = self.owner_major_col if (exchange in ("copy", "push") and columns != "canonical") else self.col_of
+        if self.local is not None and exchange in ("copy", "push"):
+            # hybrid: the nearest `direct_hops` destinations get their rows by kernel stores, the others by copies
+            self.local.set_exchange_direct(int(direct_hops))
         if exchange == "push" and self.local is not None:
             self.local.set_exchange_engine("push")  # the copy exchange with SM copies instead of the copy engines
         self._copy_done = [None, None]

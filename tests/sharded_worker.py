@@ -61,6 +61,7 @@ def main():
     ap.add_argument("--model", default="small")
     ap.add_argument("--columns", default="owner")
     ap.add_argument("--out-dtype", default="f32")
+    ap.add_argument("--direct-hops", type=int, default=0)
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     if args.backend == "nccl":
@@ -88,7 +89,7 @@ def main():
     if args.backend == "nccl":
         mod = ShardedFeatEmbed(rank, world, owner, dims, local_tables=[torch.from_numpy(tables[f]).to(dev) for f in local],
                                device=dev, chunks=args.chunks, exchange=args.exchange, out_dtype=out_dtype,
-                               columns=args.columns)
+                               columns=args.columns, direct_hops=args.direct_hops)
         lv = [torch.from_numpy(values[f]).to(dev) for f in local]
         lo = [torch.from_numpy(offsets[f]).to(dev) for f in local]
     else:

@@ -36,8 +36,8 @@ def _rank_module(cfg, tables, owner, rank, kind):
 
 @pytest.mark.parametrize("kind", ["stream", "pipe", "warp"])
 @pytest.mark.parametrize("chunks", [1, 8])
-@pytest.mark.parametrize("engine", ["copy", "push"])
-def test_copy_engine_exchange_on_one_device(kind, chunks, engine):
+@pytest.mark.parametrize("engine,direct_hops", [("copy", 0), ("push", 0), ("copy", 2), ("copy", 3)])
+def test_copy_engine_exchange_on_one_device(kind, chunks, engine, direct_hops):
     world, rows = 4, 256
     cfg, tables, values, offsets, owner = _cfg4_scaled(world, rows)
     B, units = cfg.batch, cfg.output_units
@@ -48,6 +48,7 @@ def test_copy_engine_exchange_on_one_device(kind, chunks, engine):
     for rank in range(world):
         local, mod = _rank_module(cfg, tables, owner, rank, kind)
         mod.set_exchange_engine(engine)  # who ships the pieces: the copy engines, or a small kernel
+        mod.set_exchange_direct(direct_hops)  # rows for the nearest ranks stored by the pooling kernel itself
         send = torch.full((B, mod.output_units), float("nan"), device="cuda:0")
         dv = [torch.from_numpy(values[f]).cuda() for f in local]
         do = [torch.from_numpy(offsets[f]).cuda() for f in local]

@@ -48,3 +48,9 @@ def test_sharded_bf16_rows_through_both_fused_exchanges():
     world = _world()
     _run(world, ["--exchange", "peer", "--batch", str(world * 512), "--out-dtype", "bf16"])
     _run(world, ["--exchange", "copy", "--chunks", "2", "--batch", str(world * 512), "--out-dtype", "bf16"])
+
+
+def test_sharded_hybrid_exchange_stores_to_the_nearest_rank_and_copies_to_the_rest():
+    world = _world()
+    _run(world, ["--exchange", "copy", "--chunks", "4", "--batch", str(world * 1024), "--columns", "blocks",
+                 "--direct-hops", str(max(1, world // 2))])
