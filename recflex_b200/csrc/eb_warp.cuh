@@ -20,23 +20,57 @@ struct AccPack {
   float v[V];
 };
 
-// vp points at this slot's first entry; the slot owns vp[0], vp[stride], vp[2 * stride], ...: `n_full`
-// macro-steps of U entries, then `tail` (< U) more.  A lane whose indices are all valid loads unconditionally; a
-// lane that meets a bad index takes the careful branch on its own (no warp-wide vote).
+// U consecutive indices with one load (vp is aligned to U indices).
+template <int U, bool IDX64>
+__device__ __forceinline__ void load_index_vector(const typename IdxOf<IDX64>::type* vp, typename IdxOf<IDX64>::type (&idx)[U]) {
+  if constexpr (!IDX64 && U == 4) {
+    const int4 q = __ldg(reinterpret_cast<const int4*>(vp));
+    idx[0] = q.x; idx[1] = q.y; idx[2] = q.z; idx[3] = q.w;
+  } else if constexpr (!IDX64 && U == 2) {
+    const int2 q = __ldg(reinterpret_cast<const int2*>(vp));
+    idx[0] = q.x; idx[1] = q.y;
+  } else if constexpr (IDX64 && U == 2) {
+    const longlong2 q = __ldg(reinterpret_cast<const longlong2*>(vp));
+    idx[0] = q.x; idx[1] = q.y;
+  } else {
+#pragma unroll
+    for (int u = 0; u < U; ++u) idx[u] = __ldg(vp + u);
+  }
+}
+
+// Sum of the rows vp[0 .. n): a slot's own contiguous run of the bag's entries.  Entries up to the first position
+// aligned to U indices and the ragged end go one at a time; in between every macro-step fetches its U indices with one
+// vector load.  A lane whose indices are all valid loads unconditionally; a lane that meets a bad index takes the
+// careful branch on its own (no warp-wide vote, so slots may run different numbers of steps).
 template <typename T, int V, int U, bool IDX64>
 __device__ __forceinline__ AccPack<V> bag_sum(const typename IdxOf<IDX64>::type* vp, const char* tcol,
-                                              unsigned row_bytes, unsigned long long rows, int stride, int n_full,
-                                              int tail, uint32_t* status) {
+                                              unsigned row_bytes, unsigned long long rows, int n, uint32_t* status) {
   using Ops = RowOps<T, V>;
   using IdxT = typename IdxOf<IDX64>::type;
   AccPack<V> a;
   zero_vals<V>(a.v);
   const unsigned rows32 = rows > 0x80000000ull ? 0x80000000u : (unsigned)rows;
+  auto one = [&](IdxT ix) {
+    bool ok;
+    if constexpr (IDX64) ok = (unsigned long long)ix < rows;
+    else ok = (unsigned)ix < rows32;
+    if (ok) {
+      if constexpr (IDX64) Ops::add(a.v, Ops::load(tcol + ix * (long long)row_bytes));
+      else Ops::add(a.v, Ops::load(tcol + (unsigned long long)(unsigned)ix * row_bytes));
+    } else {
+      flag(status, kStatusBadIndex);
+    }
+  };
+  int head = (int)((U - (reinterpret_cast<uintptr_t>(vp) / sizeof(IdxT)) % U) % U);
+  head = head < n ? head : n;
+  for (int u = 0; u < head; ++u) one(__ldg(vp + u));
+  vp += head;
+  n -= head;
+  const int n_full = n / U;
   for (int i = 0; i < n_full; ++i) {
     IdxT idx[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) idx[u] = __ldg(vp + u * stride);
-    vp += U * stride;
+    load_index_vector<U, IDX64>(vp, idx);
+    vp += U;
     bool valid = true;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -53,52 +87,33 @@ __device__ __forceinline__ AccPack<V> bag_sum(const typename IdxOf<IDX64>::type*
 #pragma unroll
       for (int u = 0; u < U; ++u) Ops::add(a.v, rows_[u]);
     } else {
-      flag(status, kStatusBadIndex);
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        bool ok;
-        if constexpr (IDX64) ok = (unsigned long long)idx[u] < rows;
-        else ok = (unsigned)idx[u] < rows32;
-        if (ok) {
-          if constexpr (IDX64) Ops::add(a.v, Ops::load(tcol + idx[u] * (long long)row_bytes));
-          else Ops::add(a.v, Ops::load(tcol + (unsigned long long)(unsigned)idx[u] * row_bytes));
-        }
-      }
+      for (int u = 0; u < U; ++u) one(idx[u]);
     }
   }
-  for (int u = 0; u < tail; ++u) {  // ragged end of the bag, one entry at a time
-    const IdxT ix = __ldg(vp + u * stride);
-    bool ok;
-    if constexpr (IDX64) ok = (unsigned long long)ix < rows;
-    else ok = (unsigned)ix < rows32;
-    if (ok) {
-      if constexpr (IDX64) Ops::add(a.v, Ops::load(tcol + ix * (long long)row_bytes));
-      else Ops::add(a.v, Ops::load(tcol + (unsigned long long)(unsigned)ix * row_bytes));
-    } else {
-      flag(status, kStatusBadIndex);
-    }
-  }
+  const int tail = n - n_full * U;
+  for (int u = 0; u < tail; ++u) one(__ldg(vp + u));  // ragged end, one entry at a time
   return a;
 }
 
-// One bag, one warp.
+// One bag, one warp: the warp's R slots each take a contiguous run of ceil(len / R) entries.
 template <typename T, int V, int U, bool IDX64>
 __device__ __forceinline__ void bag_warp(const FeatStatic& fs, const char* values, int64_t s, int64_t e, char* orow,
                                          int out_vec, int out_dt, uint32_t* status, int lane) {
-  const int lgG = fs.lg_group, G = 1 << lgG, R = 32 >> lgG;
+  const int lgG = fs.lg_group, G = 1 << lgG, lgR = 5 - lgG;
   const int r = lane >> lgG, cl = lane & (G - 1);
   const int len = (int)(e - s);
-  const int n_full = len / (R * U);           // macro-steps in which every slot has U entries
-  const int left = len - n_full * R * U - r;  // entries left from my first tail position on
-  const int tail = left <= 0 ? 0 : (left + R - 1) / R;
-  const typename IdxOf<IDX64>::type* vp = reinterpret_cast<const typename IdxOf<IDX64>::type*>(values) + s + r;
+  const int run = (len + (1 << lgR) - 1) >> lgR;
+  const int first = min(r * run, len);
+  const int n = min(run, len - first);
+  const typename IdxOf<IDX64>::type* vp = reinterpret_cast<const typename IdxOf<IDX64>::type*>(values) + s + first;
   for (int xc = 0; xc < fs.nx; ++xc) {
     const int cs = (xc * G + cl) * V;
     const bool col_ok = cs < fs.dim;
     AccPack<V> a;
     if (col_ok) {
       a = bag_sum<T, V, U, IDX64>(vp, fs.table + (size_t)cs * sizeof(T), (unsigned)fs.row_bytes,
-                                  (unsigned long long)fs.rows, R, n_full, tail, status);
+                                  (unsigned long long)fs.rows, n, status);
     } else {
       zero_vals<V>(a.v);
     }
