@@ -56,7 +56,8 @@ extern "C" {
  *                   (warp_per_sample_kernel.cuh:10-82) and the one-hot row copy
  *                   onehot::GatherSegments (onehot_kernel.cuh:14-87).
  *   EB_SCHED_WARP   a whole warp owns one bag; its 32/(row_bytes/16) row slots
- *                   split the bag and are combined with warp shuffles.  For
+ *                   each take a contiguous run of the bag (indices fetched 2 or
+ *                   4 at a time) and are combined with warp shuffles.  For
  *                   long, evenly sized bags.  These features are pooled by a
  *                   separate lean kernel (one CTA per 8 bags, 8 CTAs per SM, two
  *                   or four rows per lane in flight: unroll <= 2 -> 2, else 4)

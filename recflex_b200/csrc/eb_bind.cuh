@@ -13,6 +13,8 @@
 
 namespace ebk {
 
+constexpr int kTilesPerWarp = 16;  // tiles a persistent warp should get (8 and 32 measured the same on cfg3, 64 slower)
+
 // ---------------------------------------------------------------------------
 // block-wide exclusive scan of one int64 per thread (kBindThreads threads)
 // ---------------------------------------------------------------------------
@@ -108,7 +110,7 @@ __global__ void __launch_bounds__(kBindThreads) eb_bind_kernel(LaunchArgs a, int
   // ticket costs about the same whatever the feature; about 16 tiles per warp.
   // In chunked order a tile must stay inside one piece of chunk_rows bags.
   const long long piece_cap = a.chunks > 0 ? (a.chunk_rows & -a.chunk_rows) : (1ll << 30);
-  long long target = total_bytes / ((long long)a.warps_total * 16);
+  long long target = total_bytes / ((long long)a.warps_total * kTilesPerWarp);
   target = target < (16 << 10) ? (16 << 10) : (target > (256 << 10) ? (256 << 10) : target);
   for (int f = tid; f < F; f += kBindThreads) {
     const FeatStatic fs = a.feats[f];

@@ -14,15 +14,10 @@ constexpr int kMaxOccupancy = 8;        // 2048 threads per SM / 256
 constexpr int kBindThreads = 1024;
 constexpr int kPipeCellBytes = 512;      // one ring cell: 32 lanes x 16 bytes
 constexpr int kPipeMaxCells = 16;        // unroll x stages of the deepest pipelined variant
-#ifndef EB_PIPE_D2
-#define EB_PIPE_D2 4
-#define EB_PIPE_D4 3
-#define EB_PIPE_D8 2
-#endif
 // Macro-steps the pipelined schedule keeps in flight, by unroll (rows per macro-step); the ring holds unroll x depth
 // cells of 512 bytes per warp.  Batches with 64-bit indices always run the unroll-4 variant.
 __host__ __device__ constexpr inline int pipe_depth(int unroll) {
-  return unroll <= 2 ? EB_PIPE_D2 : (unroll == 4 ? EB_PIPE_D4 : EB_PIPE_D8);  // 6 and 8: two macro-steps
+  return unroll <= 2 ? 4 : (unroll == 4 ? 3 : 2);  // 6 and 8: two macro-steps
 }
 __host__ __device__ constexpr inline int pipe_cells(int unroll) {
   const int u = unroll <= 2 ? 2 : (unroll == 4 ? 4 : (unroll == 6 ? 6 : 8));
