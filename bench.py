@@ -65,7 +65,7 @@ def parse_args():
                         "the other; default: the tuned file's value, else 0)")
     p.add_argument("--kind", type=str, default="", help="force one schedule kind for every feature (debugging)")
     p.add_argument("--unroll", type=int, default=0)
-    p.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU baseline budget")
+    p.add_argument("--cpu-seconds", type=float, default=12.0, help="seconds of CPU work the CPU baseline may take")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--chunks", type=int, default=0, help="batch pieces of the sharded path (exchange/pooling overlap; default 4 for nccl, 8 for copy)")
@@ -441,7 +441,8 @@ def measure_replicated(args, dev, world, rank, local_rank):
         del tb
         _, occupancy = mod.get_schedules()
 
-    per_step_launches = 2 + (1 if any(s.kind == _lib.EB_SCHED_WARP for s in mod.get_schedules()[0]) else 0)
+    # binding kernel + fused kernel + long-bag kernel per step, + the warp-per-bag kernel when a feature is on that schedule
+    per_step_launches = 3 + (1 if any(s.kind == _lib.EB_SCHED_WARP for s in mod.get_schedules()[0]) else 0)
     for i in range(max(3, args.warmup)):
         mod.forward_packed(dev_v[i % nb], dev_o[i % nb], out=out)
     mod.check_status()
@@ -622,14 +623,13 @@ def measure_replicated(args, dev, world, rank, local_rank):
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak if achieved else None, "traffic": traffic,
                 "dram_frac": traffic / (k_ms * 1e-3) / 1e9 / peak if traffic and k_ms else None,
-                "kernel": "eb_fused_kernel (+ eb_bind_kernel" + (", eb_warp_kernel)" if per_step_launches == 3 else ")"),
+                "kernel": "eb_fused_kernel (+ eb_bind_kernel, eb_longbag_kernel" + (", eb_warp_kernel)" if per_step_launches == 4 else ")"),
                 "kernel_ms": k_ms, "algorithmic_bytes_per_launch": mean_bytes, "peak_source": peak_src,
                 "note": "frac = algorithmic bytes / kernel time / peak and may exceed 1 (popular rows hit in the 126 MB "
                         "L2); dram_frac = measured DRAM bytes of a launch / kernel time / peak",
             },
             "e2e": {"value": world * K * B / t_e2e if t_e2e else None, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": t_e2e / K * 1e3 if t_e2e else None},
-            # binding kernel + fused kernel per step, + the warp-per-bag kernel when a feature is on that schedule
             "gpu_launches": per_step_launches * K * (1 + (2 if t_e2e else 0) + (1 if t_strong else 0)),
             "clocks": sampler.summary(),
         }
