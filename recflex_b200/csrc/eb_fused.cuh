@@ -153,13 +153,24 @@ __global__ void __launch_bounds__(kCtaThreads, OCC) eb_fused_kernel(LaunchArgs a
       chunk = t / per_chunk;
       tt = t - chunk * per_chunk;
     }
-    int lo = 0, hi = F;  // tile_prefix[lo] <= tt < tile_prefix[hi]
-    while (hi - lo > 1) {
-      const int mid = (lo + hi) >> 1;
-      if ((uint32_t)__ldg(tile_prefix + mid) <= tt) lo = mid; else hi = mid;
+    // The ticket's feature: the last position of the prefix sum that is <= tt.  The warp probes 32 evenly spaced
+    // positions of the remaining range per round (two dependent loads for up to 1024 features, where a binary
+    // search makes ten); the last round, at spacing 1, fetches the feature ids along with the prefix values.
+    int lo = 0, span = F, f, k;
+    uint32_t pv;
+    while (true) {
+      const int step = (span + 31) >> 5;
+      const bool in = lane * step < span;
+      const int i = lo + lane * step;
+      pv = in ? (uint32_t)__ldg(tile_prefix + i) : 0xffffffffu;
+      f = (in && step == 1) ? __ldg(order + i) : 0;
+      k = __popc(__ballot_sync(kFull, in && pv <= tt)) - 1;  // tile_prefix[lo] <= tt, so lane 0 always votes
+      lo += k * step;
+      if (step == 1) break;
+      span = min(step, span - k * step);
     }
-    const int f = __ldg(order + lo);
-    int64_t tile = (int64_t)(tt - (uint32_t)__ldg(tile_prefix + lo));
+    f = __shfl_sync(kFull, f, k);
+    int64_t tile = (int64_t)(tt - __shfl_sync(kFull, pv, k));
     const FeatStatic fs = a.feats[f];
     const FeatDyn fd = dyn[f];
     const int n = __ldg(bpt + f);

@@ -838,6 +838,24 @@ __device__ __forceinline__ void tile_stream(const LaunchArgs& ka, const TileCtx&
         ch = load_chunk<IDX64>(c, bb, nb, lane);
       }
       const int n = ch.n;
+      // my piece [s, e_end): the first n % R slots hold one entry more
+      const int q = n >> lgR, rem = n & (R - 1);
+      const int s = r * q + min(r, rem);
+      const int e_end = s + q + (r < rem ? 1 : 0);
+      const int ls = q + (rem ? 1 : 0);  // longest piece; the shortest has q entries
+      const IdxT* vp = reinterpret_cast<const IdxT*>(c.values) + ch.e0;
+      // pipelined walk: the indices of macro-step 0 are asked for now, so that they travel while the chunk's
+      // bookkeeping below runs; `full`: every slot has U real entries there, so they are fetched without guards
+      IdxT idx[U];
+      bool full = U <= q;
+      if constexpr (D > 0) {
+        if (full) {
+#pragma unroll
+          for (int u = 0; u < U; ++u) idx[u] = __ldg(vp + s + u);
+        } else {
+          load_indices<U, IDX64>(vp, s, e_end, col_ok, idx);
+        }
+      }
       char* const orow = chunk_out(c, bb) + ((size_t)cs << (FS ? 2 : c.es_shift));
       const bool nonempty = ch.hi > ch.lo;
       const unsigned nz = __ballot_sync(kFull, nonempty);
@@ -862,11 +880,6 @@ __device__ __forceinline__ void tile_stream(const LaunchArgs& ka, const TileCtx&
       if (lane == 0) items[__popc(nz)] = make_int2(kNoEnd, 0);
       __syncwarp();
 
-      // my piece [s, e_end): the first n % R slots hold one entry more
-      const int q = n >> lgR, rem = n & (R - 1);
-      const int s = r * q + min(r, rem);
-      const int e_end = s + q + (r < rem ? 1 : 0);
-      const int ls = q + (rem ? 1 : 0);  // longest piece; the shortest has q entries
       // the bag that holds my first entry
       int kb = 0;
 #pragma unroll
@@ -884,7 +897,6 @@ __device__ __forceinline__ void tile_stream(const LaunchArgs& ka, const TileCtx&
       const int head_bag = kb;
       if (kend > e_end) kend = kNoEnd;
       int e = s;
-      const IdxT* vp = reinterpret_cast<const IdxT*>(c.values) + ch.e0;
       float acc[V];
       zero_vals<V>(acc);
 
@@ -919,16 +931,7 @@ __device__ __forceinline__ void tile_stream(const LaunchArgs& ka, const TileCtx&
       } else {
         const unsigned cell = smem_addr(ring) + lane * 16;  // my 16-byte cell of ring slot 0, entry 0
         const int nsteps = (ls + U - 1) / U;
-        IdxT idx[U];
         bool bad = false;
-        // indices of macro-step 0; `full`: every slot has U real entries there, so they were fetched without guards
-        bool full = U <= q;
-        if (full) {
-#pragma unroll
-          for (int u = 0; u < U; ++u) idx[u] = __ldg(vp + s + u);
-        } else {
-          load_indices<U, IDX64>(vp, s, e_end, col_ok, idx);
-        }
         unsigned cell_in = cell;  // ring cursors: copies go in by shared-memory address, rows come out by pointer
         const unsigned cell_end = cell + D * U * 512;
         const unsigned char* const ring_lane = ring + lane * 16;
