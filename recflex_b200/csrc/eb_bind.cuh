@@ -1,5 +1,5 @@
 // eb_bind_kernel: one CTA; turns the batch's per-feature index counts into
-// tile sizes, a heaviest-first feature order and an exclusive prefix sum of
+// tile sizes of equal estimated time, a longest-first feature order and an exclusive prefix sum of
 // tile counts: the run-time block-to-feature binding.  Replaces the host
 // GetTaskMapping (RecFlex/sched_basic_csrc/task_mapping.cu:6-18) and the
 // per-schedule num_tiles / num_blocks arithmetic of the host preprocess
@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(kBindThreads) eb_bind_kernel(LaunchArgs a, int
   }
   __syncthreads();
 
-  // pass 3: heaviest tiles first (longest-processing-time order) to shorten the tail
+  // pass 3: longest tiles first (longest-processing-time order) to shorten the tail
   for (int f = tid; f < F; f += kBindThreads) {
     int rank = f;
     if (F <= kMaxLptFeatures) {

@@ -1,9 +1,9 @@
-// (Features on the warp-per-bag schedule get no tiles here: eb_warp_kernel, eb_warp.cuh, pools them.)
 // eb_fused_kernel: persistent CTAs; every warp draws tile tickets, finds the
-// ticket's feature by binary search in the prefix sum that eb_bind_kernel
+// ticket's feature with a 32-way search in the prefix sum that eb_bind_kernel
 // (eb_bind.cuh) left in the workspace and runs that feature's schedule.
 // Replaces the generated FusedKnl dispatcher
 // (RecFlex/code_emitter/codegen.py:318-383).
+// (Features on the warp-per-bag schedule get no tiles here: eb_warp_kernel, eb_warp.cuh, pools them.)
 #pragma once
 #include "eb_common.cuh"
 #include "eb_schedules.cuh"
