@@ -296,6 +296,31 @@ def test_random_models_every_kind():
                                    err_msg=f"trial {trial}: {[(t.shape, t.dtype) for t in tables]} {scheds}")
 
 
+@pytest.mark.parametrize("F", [1, 31, 32, 33, 1100])
+def test_feature_counts_around_the_ticket_search_rounds(F):
+    """The ticket's feature is found by probing 32 positions of the tile prefix sum per round: one round up to 32
+    features, two up to 1024, three beyond.  Features on the warp-per-bag schedule own no tiles of the fused kernel, so
+    the prefix sum holds runs of equal values that the search has to step over."""
+    rng = np.random.default_rng(77 + F)
+    batch = 70
+    tables, values, offsets, scheds = [], [], [], []
+    for f in range(F):
+        dim = int(rng.choice([4, 8, 16, 32]))
+        rows = int(rng.integers(4, 200))
+        tables.append((rng.standard_normal((rows, dim)) * 0.1).astype(np.float32))
+        lens = rng.integers(0, 6, batch)
+        o = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+        offsets.append(o)
+        values.append(rng.integers(0, rows, o[-1]).astype(np.int32))
+        scheds.append(Schedule("warp" if f % 5 == 3 else str(rng.choice(["pipe", "stream", "group"])), 4))
+    mod = FeatEmbed("cuda:0", embed_tables=device_tables(tables))
+    mod.set_schedules(scheds, occupancy=4)
+    out = mod(to_device(values), to_device(offsets))
+    mod.check_status()
+    expect = oracle.pool(tables, values, offsets, acc64=True)
+    np.testing.assert_allclose(out.cpu().numpy(), expect, rtol=1e-5, atol=1e-6)
+
+
 @pytest.mark.parametrize("dtype", [np.int32, np.int64])
 def test_offsets_from_lengths_on_device(cfg1, dtype):
     cfg, tables, values, offsets, mod = cfg1
